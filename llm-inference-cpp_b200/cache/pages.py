@@ -67,15 +67,21 @@ class PagePool:
     ``window`` > 0 means a query only needs the last ``window`` positions: pages that lie
     wholly before the window of the next token are given back early and their table entries
     become -1.
+
+    ``every`` > 1 means the group keeps one row per ``every`` positions (row b once position ``b * every + every - 1``
+    is there: a summary of a block of positions): lengths are still counted in positions, pages in rows.
     """
 
     def __init__(self, n_pages: int, page_size: int = PAGE_SIZE, window: int = 0, n_slots: int = 0,
-                 max_pages_per_slot: int = 0):
+                 max_pages_per_slot: int = 0, every: int = 1):
         if n_pages <= 0:
             raise CacheError("cache: needs at least one page")
+        if every < 1 or (every > 1 and window > 0):
+            raise CacheError("cache: a group of one row per block of positions has no window")
         self.n_pages = n_pages
         self.page_size = page_size
         self.window = window
+        self.every = every
         self._free = list(range(n_pages - 1, -1, -1))
         self._pages: dict[int, list[int]] = {}     # slot -> page ids by position (-1: released)
         self._length: dict[int, int] = {}
@@ -109,9 +115,13 @@ class PagePool:
             self.matrix[slot, :] = -1
 
     # -- growth ----------------------------------------------------------------------------
+    def rows(self, n_positions: int) -> int:
+        """Rows the group holds for a sequence of that many positions."""
+        return n_positions // self.every
+
     def pages_needed(self, slot: int, n_new: int) -> int:
         have = len(self._pages[slot])
-        return max(0, pages_for(self._length[slot] + n_new, self.page_size) - have)
+        return max(0, pages_for(self.rows(self._length[slot] + n_new), self.page_size) - have)
 
     def releasable(self, slot: int) -> int:
         """Pages of a slot that lie wholly before the window of its NEXT position: what its next growth gives
@@ -135,7 +145,10 @@ class PagePool:
         ``slots`` the exact count for these slots — after a long prompt that can be several at once —, without
         them the one page that falls out when the window's start crosses a page end)."""
         import numpy as np
-        takes = (bases % self.page_size) == 0
+        if self.every > 1:       # the position completes a block whose row opens a page
+            takes = (((bases + 1) % self.every) == 0) & (((bases // self.every) % self.page_size) == 0)
+        else:
+            takes = (bases % self.page_size) == 0
         if self.window <= 0:
             gives = np.zeros(len(bases), dtype=np.int64)
         elif slots is not None:
@@ -174,7 +187,9 @@ class PagePool:
         n = self._length[slot] - 1
         if n < 0:
             raise CacheError(f"cache: slot {slot} holds no position to take back")
-        if n % self.page_size == 0:            # the position opened a page: the page goes back to where it came from
+        opened = (n % self.page_size == 0) if self.every == 1 else (
+            self.rows(n + 1) > self.rows(n) and self.rows(n) % self.page_size == 0)
+        if opened:                             # the position opened a page: the page goes back to where it came from
             page = self._pages[slot].pop()
             self._free.append(page)
             i = len(self._pages[slot])

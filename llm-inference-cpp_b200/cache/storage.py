@@ -34,6 +34,7 @@ class KVRequest:
     values: bool = True      # False: keys only (a mixer whose values are part of its key rows)
     v_heads: int = 0         # value heads and their size, where they differ from the keys' (0: as the keys)
     v_dim: int = 0
+    every: int = 1           # > 1: one row per block of that many positions (row b once the block's last position is there)
 
 
 @dataclass(frozen=True)
@@ -60,7 +61,10 @@ class KVGroup:
         self.request = request
         self.n_calls = n_calls
         self.page_size = page_size
-        self.pool = PagePool(n_pages, page_size, request.window, n_slots, max_pages_per_slot)
+        self.every = max(1, int(request.every))
+        if self.every > 1:       # a page of rows spans `every` pages of positions; every live sequence may hold a partly filled one
+            n_pages = min(n_pages, -(-n_pages // self.every) + max(1, n_slots if n_slots > 0 else n_pages))
+        self.pool = PagePool(n_pages, page_size, request.window, n_slots, max_pages_per_slot, self.every)
         shape = (n_calls, n_pages, request.n_kv_heads, page_size, request.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v_heads, self.v_dim = request.v_heads or request.n_kv_heads, request.v_dim or request.head_dim
@@ -70,7 +74,7 @@ class KVGroup:
     def bytes_per_token(self) -> int:
         r = self.request
         per = r.n_kv_heads * r.head_dim + (self.v_heads * self.v_dim if r.values else 0)
-        return self.n_calls * per * self.k.element_size()
+        return self.n_calls * per * self.k.element_size() // self.every
 
 
 class StateGroup:

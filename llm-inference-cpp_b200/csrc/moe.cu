@@ -1,13 +1,18 @@
 // Routed experts: each token runs `top` of E small gated feed-forwards, chosen by the largest router logits, and
 // adds their outputs weighted by the softmax over the CHOSEN logits only.
 //
-//   llmi_moe_route    per token: the `top` largest of E fp32 logits (ties: the lower index), their softmax (fp32)
-//   llmi_moe_up       per (token, choice): a = act(Wg_e h) * (Wu_e h)                      [T, top, F] fp32
+//   llmi_moe_route    per token: the `top` largest of E fp32 logits (ties: the lower index), their softmax (fp32);
+//                     or (`mode` 1) scores s = logistic(logit), the `top` largest scores weighted by s / (sum of the
+//                     chosen s + 1e-20), optionally among the experts of the best `keep` of `n_groups` equal runs of
+//                     neighbouring experts only, a run's score being the sum of its two largest scores
+//   llmi_moe_up       per (token, choice): a = act(Wg_e h) * (Wu_e h), or a = act(Wu_e h) for experts
+//                     without a gate matrix                                                  [T, top, F] fp32
 //   llmi_moe_down     per token: y = sum over its choices, in the order of the choice, of weight * (Wd_e a)   [T, W] fp32
 // The two product kernels stream an expert's rows once per (token, choice): the form for a handful of tokens (a
 // decode step), where every chosen expert's weights are read once or a few times anyway.  Each output is one
 // warp's sum in a fixed order, so a token's result does not depend on the batch it is in.
-// Weights are stacked by expert: Wg, Wu [E, F, W], Wd [E, W, F], in the compute type; act: 0 silu, 1 tanh-GELU.
+// Weights are stacked by expert: Wg, Wu [E, F, W], Wd [E, W, F], in the compute type; act: 0 silu, 1 tanh-GELU,
+// 2 the square of relu.
 #include <math.h>
 
 #include "common.cuh"
@@ -16,10 +21,21 @@ namespace llmi {
 
 constexpr int MOE_MAX_PER_LANE = 8;      // experts per lane: E <= 256
 
-// One warp per token.
+// The warp's best (value, index) pair; ties go to the lower index.  Every lane gets it.
+__device__ __forceinline__ void warp_best(float& best, int& best_e) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+    if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+  }
+}
+
+// One warp per token.  MODE 0: softmax over the chosen logits.  MODE 1: logistic scores, normalised over the chosen.
+template <int MODE>
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, long ld, int E, int top, const int32_t* __restrict__ tok_seq,
-                 int32_t* __restrict__ idx, float* __restrict__ wt, int n_tokens) {
+moe_route_kernel(const float* __restrict__ logits, long ld, int E, int top, int n_groups, int keep,
+                 const int32_t* __restrict__ tok_seq, int32_t* __restrict__ idx, float* __restrict__ wt, int n_tokens) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -33,8 +49,43 @@ moe_route_kernel(const float* __restrict__ logits, long ld, int E, int top, cons
   for (int i = 0; i < MOE_MAX_PER_LANE; ++i) {
     const int e = lane + 32 * i;
     v[i] = e < E ? logits[(size_t)t * ld + e] : -INFINITY;
+    if (MODE == 1 && e < E) v[i] = 1.0f / (1.0f + expf(-v[i]));
   }
-  float first = 0.f, denom = 0.f, mine = 0.f;      // lane j keeps choice j's exp (top <= 32)
+  if (n_groups > 1 && keep < n_groups) {
+    // lane g keeps the score of run g (n_groups <= 32): the sum of its two largest scores
+    const int per = E / n_groups;
+    float mine_g = -INFINITY;
+    for (int g = 0; g < n_groups; ++g) {
+      float total = 0.f;
+      int taken = -1;
+      for (int r = 0; r < 2 && r < per; ++r) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < MOE_MAX_PER_LANE; ++i) {
+          const int e = lane + 32 * i;
+          if (e < E && e / per == g && e != taken && (v[i] > best || (v[i] == best && e < best_e))) { best = v[i]; best_e = e; }
+        }
+        warp_best(best, best_e);
+        total += best;
+        taken = best_e;
+      }
+      if (lane == g) mine_g = total;
+    }
+    uint32_t kept = 0u;
+    for (int j = 0; j < keep; ++j) {
+      float best = (kept >> lane) & 1u ? -INFINITY : mine_g;
+      int best_g = lane < n_groups && !((kept >> lane) & 1u) ? lane : 0x7fffffff;
+      warp_best(best, best_g);
+      kept |= 1u << best_g;
+    }
+#pragma unroll
+    for (int i = 0; i < MOE_MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E && !((kept >> (e / per)) & 1u)) v[i] = -INFINITY;
+    }
+  }
+  float first = 0.f, denom = 0.f, mine = 0.f;      // lane j keeps choice j's weight before the division (top <= 32)
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
@@ -43,14 +94,9 @@ moe_route_kernel(const float* __restrict__ logits, long ld, int E, int top, cons
       const int e = lane + 32 * i;
       if (e < E && (v[i] > best || (v[i] == best && e < best_e))) { best = v[i]; best_e = e; }   // (a taken one is -inf: it never wins while a free one is left)
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-    }
+    warp_best(best, best_e);
     if (j == 0) first = best;                        // the largest logit: the softmax's shift
-    const float ex = expf(best - first);
+    const float ex = MODE == 1 ? best : expf(best - first);
     denom += ex;
     if (lane == j) mine = ex;
     if (lane == 0) idx[(size_t)t * top + j] = best_e;
@@ -58,11 +104,12 @@ moe_route_kernel(const float* __restrict__ logits, long ld, int E, int top, cons
     for (int i = 0; i < MOE_MAX_PER_LANE; ++i)
       if (lane + 32 * i == best_e) v[i] = -INFINITY;   // taken
   }
-  if (lane < top) wt[(size_t)t * top + lane] = mine / denom;
+  if (lane < top) wt[(size_t)t * top + lane] = MODE == 1 ? mine / (denom + 1e-20f) : mine / denom;
 }
 
 template <int ACT> __device__ __forceinline__ float moe_act(float g) {
   if (ACT == 0) return g / (1.0f + expf(-g));
+  if (ACT == 2) { g = fmaxf(g, 0.f); return g * g; }
   return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
 }
 
@@ -103,7 +150,7 @@ __device__ __forceinline__ float warp_dot(const float* __restrict__ x_s, const T
   return warp_sum(acc);
 }
 
-// grid (T * top, ceil(F / 8)); 8 warps, one output f per warp.
+// grid (T * top, ceil(F / 8)); 8 warps, one output f per warp.  wg null: experts without a gate matrix, a = act(Wu h).
 template <typename T, int ACT, bool VEC>
 __global__ void __launch_bounds__(256)
 moe_up_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ wg, const T* __restrict__ wu, int W, int F, int top,
@@ -119,8 +166,12 @@ moe_up_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ wg, const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f = blockIdx.y * 8 + warp;
   if (f >= F) return;
-  const float g = warp_dot<T, VEC>(h_s, wg + ((size_t)e * F + f) * W, W, lane);
   const float u = warp_dot<T, VEC>(h_s, wu + ((size_t)e * F + f) * W, W, lane);
+  if (wg == nullptr) {
+    if (lane == 0) a[(size_t)item * F + f] = moe_act<ACT>(u);
+    return;
+  }
+  const float g = warp_dot<T, VEC>(h_s, wg + ((size_t)e * F + f) * W, W, lane);
   if (lane == 0) a[(size_t)item * F + f] = moe_act<ACT>(g) * u;
 }
 
@@ -152,10 +203,19 @@ moe_down_kernel(const float* __restrict__ a, const T* __restrict__ wd, int W, in
 
 using namespace llmi;
 
-LLMI_EXPORT int llmi_moe_route(const float* logits, long ld, int E, int top, const int32_t* tok_seq, int32_t* idx, float* wt,
-                               int n_tokens, cudaStream_t stream) {
+// mode 0: softmax over the chosen logits; mode 1: logistic scores normalised over the chosen.  n_groups <= 1 or
+// keep >= n_groups: every expert can be chosen.
+LLMI_EXPORT int llmi_moe_route(const float* logits, long ld, int E, int top, int mode, int n_groups, int keep,
+                               const int32_t* tok_seq, int32_t* idx, float* wt, int n_tokens, cudaStream_t stream) {
   if (n_tokens <= 0 || E <= 0 || top <= 0 || top > E || top > 32 || E > 32 * MOE_MAX_PER_LANE) return LLMI_ERR_BAD_SIZE;
-  return launch_pdl(PDL_SMALL, moe_route_kernel, (n_tokens + 3) / 4, 128, 0, stream, logits, ld, E, top, tok_seq, idx, wt, n_tokens);
+  if (n_groups > 1 && (n_groups > 32 || E % n_groups != 0 || keep < 1 || keep * (E / n_groups) < top)) return LLMI_ERR_BAD_SIZE;
+  if (mode == 0)
+    return launch_pdl(PDL_SMALL, moe_route_kernel<0>, (n_tokens + 3) / 4, 128, 0, stream, logits, ld, E, top, n_groups, keep, tok_seq,
+                      idx, wt, n_tokens);
+  if (mode == 1)
+    return launch_pdl(PDL_SMALL, moe_route_kernel<1>, (n_tokens + 3) / 4, 128, 0, stream, logits, ld, E, top, n_groups, keep, tok_seq,
+                      idx, wt, n_tokens);
+  return LLMI_ERR_UNSUPPORTED;
 }
 
 template <typename T, int ACT, bool VEC>
@@ -189,14 +249,16 @@ static int launch_moe_down(const float* a, const void* wd, int W, int F, int top
 LLMI_EXPORT int llmi_moe_up(int dtype, const void* h, long ldh, const void* wg, const void* wu, int W, int F, int top,
                             const int32_t* idx, float* a, int act, int n_tokens, cudaStream_t stream) {
   if (n_tokens <= 0 || W <= 0 || F <= 0 || top <= 0 || (size_t)W * 4 > 160 * 1024 || (F + 7) / 8 > 65535) return LLMI_ERR_BAD_SIZE;
-  if (act != 0 && act != 1) return LLMI_ERR_UNSUPPORTED;
+  if (act < 0 || act > 2) return LLMI_ERR_UNSUPPORTED;
   const int esz = dtype == LLMI_DTYPE_F32 ? 4 : 2;
   const bool vec = ((size_t)W * esz) % 16 == 0 && !((uintptr_t)wg & 15) && !((uintptr_t)wu & 15);
 #define LLMI_UP(T, ACT) \
   return vec ? launch_moe_up<T, ACT, true>(h, ldh, wg, wu, W, F, top, idx, a, n_tokens, stream) \
              : launch_moe_up<T, ACT, false>(h, ldh, wg, wu, W, F, top, idx, a, n_tokens, stream)
-  if (dtype == LLMI_DTYPE_F32) { if (act == 0) LLMI_UP(float, 0); else LLMI_UP(float, 1); }
-  if (dtype == LLMI_DTYPE_BF16) { if (act == 0) LLMI_UP(__nv_bfloat16, 0); else LLMI_UP(__nv_bfloat16, 1); }
+  if (dtype == LLMI_DTYPE_F32) { if (act == 0) LLMI_UP(float, 0); else if (act == 1) LLMI_UP(float, 1); else LLMI_UP(float, 2); }
+  if (dtype == LLMI_DTYPE_BF16) {
+    if (act == 0) LLMI_UP(__nv_bfloat16, 0); else if (act == 1) LLMI_UP(__nv_bfloat16, 1); else LLMI_UP(__nv_bfloat16, 2);
+  }
 #undef LLMI_UP
   return LLMI_ERR_BAD_DTYPE;
 }

@@ -5,6 +5,7 @@
 //   llmi_moe_group       one block: items per expert, their offsets, the items in expert order, where each item went,
 //                        and the list of 64-row tiles (expert, first row) that the product kernels walk
 //   llmi_moe_up_grouped  tile x 64 columns: a = act(h Wgᵀ) * (h Wuᵀ) for the tile's gathered token rows   -> bf16 [items, F]
+//                        (experts without a gate matrix, wg null: a = act(h Wuᵀ))
 //   llmi_moe_down_grouped tile x 64 columns: y = a Wdᵀ                                                     -> fp32 [items, W]
 //   llmi_moe_combine     per token: sum over its choices, in the order of the choice, of weight * y[item]   -> fp32 [T, W]
 // mma.sync m16n8k16 (bf16 in, fp32 accumulate), operands by cp.async through three stages of 64 k.  A row's result does not
@@ -65,6 +66,7 @@ moe_group_kernel(const int32_t* __restrict__ idx, int n_items, int E, int32_t* _
 
 // MODE 0: A rows are gathered token rows (item / top) of h, two weight matrices (gate, up), out = act(g) * u in bf16.
 // MODE 1: A rows are the sorted rows themselves, one weight matrix, out = fp32.
+// MODE 3: as MODE 0 for experts without a gate matrix: one weight matrix, out = act(h Wuᵀ) in bf16.
 // MODE 2: no experts — a batch of equal products, one per head (blockIdx.z): A rows are the M rows of x from column
 //         b * a_batch on, the weight is B0[b], out (bf16) goes to column b * o_batch on.
 template <int MODE, int ACT>
@@ -100,7 +102,7 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ A, long lda, const int32_t*
     slot_c[i] = (s % GB_CH) * 8;
     const int r = slot_r[i];
     if (r < rows_here) {
-      const long src_row = MODE == 0 ? (long)(sorted_items[row0 + r] / top) : (long)(row0 + r);
+      const long src_row = (MODE == 0 || MODE == 3) ? (long)(sorted_items[row0 + r] / top) : (long)(row0 + r);
       a_src[i] = A + src_row * lda + (MODE == 2 ? (long)e * a_batch : 0L);
     } else {
       a_src[i] = nullptr;
@@ -186,6 +188,13 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ A, long lda, const int32_t*
           __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)(row0 + r) * ldo + (size_t)e * o_batch + c;
           if (c + 1 < N) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);
           else dst[0] = __float2bfloat16_rn(v0);
+        } else if (MODE == 3) {
+          const float r0 = fmaxf(v0, 0.f), r1 = fmaxf(v1, 0.f);
+          const float a0 = ACT == 2 ? r0 * r0 : ACT == 0 ? v0 / (1.0f + expf(-v0)) : 0.5f * v0 * (1.0f + tanhf(0.7978845608028654f * (v0 + 0.044715f * v0 * v0 * v0)));
+          const float a1 = ACT == 2 ? r1 * r1 : ACT == 0 ? v1 / (1.0f + expf(-v1)) : 0.5f * v1 * (1.0f + tanhf(0.7978845608028654f * (v1 + 0.044715f * v1 * v1 * v1)));
+          __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)(row0 + r) * ldo + c;
+          if (c + 1 < N) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a0, a1);
+          else dst[0] = __float2bfloat16_rn(a0);
         } else if (MODE == 0) {
           const float u0 = acc[NB - 1][mi][nt][2 * half], u1 = acc[NB - 1][mi][nt][2 * half + 1];
           const float a0 = ACT == 0 ? v0 / (1.0f + expf(-v0)) : 0.5f * v0 * (1.0f + tanhf(0.7978845608028654f * (v0 + 0.044715f * v0 * v0 * v0)));
@@ -237,7 +246,7 @@ LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const 
   if ((W % 8) || (F % 8) || (ldh % 8) || ((uintptr_t)h & 15) || ((uintptr_t)wg & 15) || ((uintptr_t)wu & 15) || ((uintptr_t)wd & 15) ||
       ((uintptr_t)a_sorted & 15))
     return LLMI_ERR_ALIGN;
-  if (act != 0 && act != 1) return LLMI_ERR_UNSUPPORTED;
+  if (act < 0 || act > 2 || (act == 2 && wg)) return LLMI_ERR_UNSUPPORTED;
   const int n_items = n_tokens * top;
   if (scratch_ints < llmi_moe_group_ints(n_items, E)) return LLMI_ERR_BAD_SIZE;
   const int max_tiles = (n_items + GB_M - 1) / GB_M + E;
@@ -260,9 +269,19 @@ LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const 
     cudaFuncSetAttribute(moe_grouped_kernel<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
     cudaFuncSetAttribute(moe_grouped_kernel<0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
     cudaFuncSetAttribute(moe_grouped_kernel<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
+    cudaFuncSetAttribute(moe_grouped_kernel<3, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
+    cudaFuncSetAttribute(moe_grouped_kernel<3, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
+    cudaFuncSetAttribute(moe_grouped_kernel<3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
     configured.here() = true;
   }
-  if (act == 0)
+  if (!wg) {
+#define LLMI_UNGATED(ACT)                                                                                                            \
+    rc = launch_pdl(PDL_GEMM, moe_grouped_kernel<3, ACT>, grid_up, dim3(128), smem_down, stream, hb, ldh, (const int32_t*)sorted_items, \
+                    top, u, u, F, W, (const int32_t*)offsets, (const int32_t*)tile_expert, (const int32_t*)tile_row0,                 \
+                    (const int32_t*)n_tiles, a_sorted, (long)F, 0, 0L, 0L)
+    if (act == 0) LLMI_UNGATED(0); else if (act == 1) LLMI_UNGATED(1); else LLMI_UNGATED(2);
+#undef LLMI_UNGATED
+  } else if (act == 0)
     rc = launch_pdl(PDL_GEMM, moe_grouped_kernel<0, 0>, grid_up, dim3(128), smem_up, stream, hb, ldh, (const int32_t*)sorted_items, top,
                     g, u, F, W, (const int32_t*)offsets, (const int32_t*)tile_expert, (const int32_t*)tile_row0,
                     (const int32_t*)n_tiles, a_sorted, (long)F, 0, 0L, 0L);

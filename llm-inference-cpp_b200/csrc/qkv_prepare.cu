@@ -4,10 +4,12 @@
 // for a layer that reads another layer's keys and values).  Per token, in this order:
 //   * optionally an RMS norm over the WHOLE q part (all heads at once) with a weight per entry, and the same over
 //     the whole k part:  y = x / sqrt(mean(x^2) + eps) * w;
-//   * optionally the rotation of the first rot_dims entries of every q and k head, pairs (i, i + rot_dims/2), by the
-//     angle float(pos) * inv_freq[i];
+//   * optionally the rotation of the first rot_dims entries of every q and k head by the angle float(pos) * inv_freq[i]:
+//     pairs (i, i + rot_dims/2) (`pairing` 0) or neighbours (2i, 2i + 1) (`pairing` 1), cos and sin both times
+//     `amplitude` (1: a plain rotation);
 //   * q goes to `q_out` in the compute type; k and v go to the cache pages of (sequence, position).
-// Keys and values may differ in their number of heads and in their head size (two page layouts).
+// Keys and values may differ in their number of heads and in their head size (two page layouts).  With `v_from_k`
+// the row has no v part: the values are the key rows as projected (after the norm, before the rotation), head for head.
 // All arithmetic is fp32; one block per token.
 #include "common.cuh"
 #include "step_meta.cuh"
@@ -15,22 +17,32 @@
 namespace llmi {
 
 // One part (q or k) of a row: scale, weight, rotation; element e of head hd goes to dst(head) + e.
-template <typename T, typename Dst>
+struct NoCopy {
+  __device__ __forceinline__ void* operator()(int) const { return nullptr; }
+};
+
+// `plain(head)`: where the head's entries go as they are before the rotation (the values of a layer whose values are
+// its keys), or null.
+template <typename T, typename Dst, typename Plain>
 __device__ __forceinline__ void prepare_part(const float* __restrict__ src, int n_heads, int dk, float sc,
                                              const float* __restrict__ w, const float* __restrict__ inv_freq, int rot_dims,
-                                             int pos, Dst dst) {
+                                             int pairing, float amplitude, int pos, Dst dst, Plain plain) {
   const int half = rot_dims / 2, n = n_heads * dk;
   for (int idx = threadIdx.x; idx < n; idx += blockDim.x) {
     const int hd = idx / dk, e = idx - hd * dk;
     T* o = dst(hd);
+    T* pl = (T*)plain(hd);
+    if (pl) pl[e] = from_f32<T>(w ? w[idx] * (src[idx] * sc) : src[idx] * sc);
     if (e < half) {
       float s, c;
       sincosf((float)pos * inv_freq[e], &s, &c);
-      const int j = idx + half;
-      const float a = w ? w[idx] * (src[idx] * sc) : src[idx] * sc;
-      const float b = w ? w[j] * (src[j] * sc) : src[j] * sc;
-      o[e] = from_f32<T>(rot_lo(a, b, c, s));
-      o[e + half] = from_f32<T>(rot_hi(a, b, c, s));
+      s *= amplitude;
+      c *= amplitude;
+      const int i0 = pairing ? idx + e : idx, i1 = pairing ? idx + e + 1 : idx + half;      // (idx + e = head start + 2e)
+      const float a = w ? w[i0] * (src[i0] * sc) : src[i0] * sc;
+      const float b = w ? w[i1] * (src[i1] * sc) : src[i1] * sc;
+      o[pairing ? 2 * e : e] = from_f32<T>(rot_lo(a, b, c, s));
+      o[pairing ? 2 * e + 1 : e + half] = from_f32<T>(rot_hi(a, b, c, s));
     } else if (e >= rot_dims) {
       o[e] = from_f32<T>(w ? w[idx] * (src[idx] * sc) : src[idx] * sc);
     }
@@ -41,7 +53,8 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 qkv_prepare_kernel(const float* __restrict__ proj, long ld, int n_q_heads, int n_k_heads, int dk, int n_v_heads, int dv,
                    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
-                   const float* __restrict__ inv_freq, int rot_dims, const int32_t* __restrict__ tok_seq,
+                   const float* __restrict__ inv_freq, int rot_dims, int pairing, float amplitude, int v_from_k,
+                   const int32_t* __restrict__ tok_seq,
                    const int32_t* __restrict__ tok_pos, PagedKV kp, PagedKV vp, T* __restrict__ k_cache,
                    T* __restrict__ v_cache, T* __restrict__ q_out, long ldq, int has_kv, int write_kv) {
   __shared__ float scratch[32];
@@ -63,7 +76,8 @@ qkv_prepare_kernel(const float* __restrict__ proj, long ld, int n_q_heads, int n
     for (int i = threadIdx.x; i < Nq; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
     sq = 1.0f / sqrtf(block_sum(ss, scratch) / (float)Nq + eps);
   }
-  prepare_part<T>(row, n_q_heads, dk, sq, q_norm_w, inv_freq, rot_dims, pos, [&](int hd) { return qo + (size_t)hd * dk; });
+  prepare_part<T>(row, n_q_heads, dk, sq, q_norm_w, inv_freq, rot_dims, pairing, amplitude, pos,
+                  [&](int hd) { return qo + (size_t)hd * dk; }, NoCopy());
   if (!has_kv || !write_kv) return;
   const float* krow = row + Nq;
   if (k_norm_w) {
@@ -71,8 +85,14 @@ qkv_prepare_kernel(const float* __restrict__ proj, long ld, int n_q_heads, int n
     for (int i = threadIdx.x; i < Nk; i += blockDim.x) ss = fmaf(krow[i], krow[i], ss);
     sk = 1.0f / sqrtf(block_sum(ss, scratch) / (float)Nk + eps);
   }
-  prepare_part<T>(krow, n_k_heads, dk, sk, k_norm_w, inv_freq, rot_dims, pos,
-                  [&](int hd) { return k_cache + kv_row_offset(kp, seq, pos, hd); });
+  if (v_from_k) {
+    prepare_part<T>(krow, n_k_heads, dk, sk, k_norm_w, inv_freq, rot_dims, pairing, amplitude, pos,
+                    [&](int hd) { return k_cache + kv_row_offset(kp, seq, pos, hd); },
+                    [&](int hd) { return (void*)(v_cache + kv_row_offset(vp, seq, pos, hd)); });
+    return;
+  }
+  prepare_part<T>(krow, n_k_heads, dk, sk, k_norm_w, inv_freq, rot_dims, pairing, amplitude, pos,
+                  [&](int hd) { return k_cache + kv_row_offset(kp, seq, pos, hd); }, NoCopy());
   const float* vrow = krow + Nk;
   for (int idx = threadIdx.x; idx < Nv; idx += blockDim.x) {
     const int hd = idx / dv, e = idx - hd * dv;
@@ -86,21 +106,23 @@ using namespace llmi;
 
 LLMI_EXPORT int llmi_qkv_prepare(int dtype, const float* proj, long ld, int n_q_heads, int n_k_heads, int dk, int n_v_heads,
                                  int dv, const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq,
-                                 int rot_dims, const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* k_pages,
+                                 int rot_dims, int pairing, float amplitude, int v_from_k, const int32_t* tok_seq,
+                                 const int32_t* tok_pos, const int32_t* k_pages,
                                  int k_pages_stride, const int32_t* v_pages, int v_pages_stride, int page_size, void* k_cache,
                                  void* v_cache, void* q_out, long ldq, int n_tokens, int has_kv, int write_kv,
                                  cudaStream_t stream) {
   if (n_tokens <= 0 || n_q_heads <= 0 || dk <= 0 || page_size <= 0) return LLMI_ERR_BAD_SIZE;
   if (has_kv && (n_k_heads <= 0 || n_v_heads <= 0 || dv <= 0)) return LLMI_ERR_BAD_SIZE;
   if (rot_dims < 0 || rot_dims > dk || (rot_dims & 1) || (rot_dims > 0 && !inv_freq)) return LLMI_ERR_BAD_SIZE;
+  if (v_from_k && (!has_kv || n_v_heads != n_k_heads || dv != dk)) return LLMI_ERR_BAD_SIZE;
   const PagedKV kp{k_pages, k_pages_stride, page_size, n_k_heads, dk}, vp{v_pages, v_pages_stride, page_size, n_v_heads, dv};
   if (dtype == LLMI_DTYPE_F32)
     return launch_pdl(PDL_SMALL, qkv_prepare_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, proj, ld, n_q_heads, n_k_heads,
-                      dk, n_v_heads, dv, q_norm_w, k_norm_w, eps, inv_freq, rot_dims, tok_seq, tok_pos, kp, vp, (float*)k_cache,
+                      dk, n_v_heads, dv, q_norm_w, k_norm_w, eps, inv_freq, rot_dims, pairing, amplitude, v_from_k, tok_seq, tok_pos, kp, vp, (float*)k_cache,
                       (float*)v_cache, (float*)q_out, ldq, has_kv, write_kv);
   if (dtype == LLMI_DTYPE_BF16)
     return launch_pdl(PDL_SMALL, qkv_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, stream, proj, ld, n_q_heads,
-                      n_k_heads, dk, n_v_heads, dv, q_norm_w, k_norm_w, eps, inv_freq, rot_dims, tok_seq, tok_pos, kp, vp,
+                      n_k_heads, dk, n_v_heads, dv, q_norm_w, k_norm_w, eps, inv_freq, rot_dims, pairing, amplitude, v_from_k, tok_seq, tok_pos, kp, vp,
                       (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (__nv_bfloat16*)q_out, ldq, has_kv, write_kv);
   return LLMI_ERR_BAD_DTYPE;
 }

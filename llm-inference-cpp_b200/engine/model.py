@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..cache.storage import CacheBinding, KVRequest, SequenceCache, StateRequest
-from ..parts.build import build_entries, build_parts, expected_tensors
+from ..parts.build import build_entries, build_exits, build_parts, expected_tensors
 from ..parts.spec import ModelSpec
 from .batch import SequenceStep, StepBuffers, plan_step
 from ..ops import kernels
@@ -33,6 +33,8 @@ class Model:
                 raise ValueError(f"schedule call {i} reads the cache of call {call.cache_of}, which does not exist")
         self.entries = build_entries(spec, tensors, self.rt)      # what acts on the stream right before a call
         self.keeps_embedding_output = any(getattr(e, "needs_embedding_output", False) for e in self.entries)
+        self.exits = build_exits(spec, tensors, self.rt)          # what acts on the stream right behind a call
+        self.keeps_history = any(e is not None for e in self.exits)
         self.buffers = StepBuffers(self.rt.device, self.rt)
         self._graphs = None
         self._prompt_graphs = None
@@ -42,7 +44,7 @@ class Model:
         parts = [self.embedding, self.final_norm, self.head]
         for layer in self.layers:
             parts += [layer.block, *layer.parts.values()]
-        parts += [e for e in self.entries if e is not None]
+        parts += [e for e in self.entries if e is not None] + [e for e in self.exits if e is not None]
         self.pads_prompts = dtype == torch.bfloat16 and all(getattr(p, "takes_padding_rows", False) for p in parts)
         self.last_logits = None      # fp32 [rows, vocab] of the latest step_and_choose (scratch: valid until the next step)
         self.parameter_count = sum(int(tensors[n].numel()) if n in tensors else 0 for n in expected_tensors(spec))
@@ -96,8 +98,15 @@ class Model:
         more_places = []
         for i, call in enumerate(self.spec.schedule):
             layer = self.layers[call.layer]
-            more_places.append({slot: take(p.cache_request(), (i, slot)) for slot, p in layer.parts.items()
-                                if slot != "mixer" and hasattr(p, "cache_request")})
+            places = {slot: take(p.cache_request(), (i, slot)) for slot, p in layer.parts.items()
+                      if slot != "mixer" and hasattr(p, "cache_request")}
+            # what the mixer keeps beside its main request (rows that sum up blocks of positions, say); a call that
+            # reads another call's cache reads that call's main entries only and keeps these of its own
+            for name, req in (layer.mixer.more_cache_requests() if hasattr(layer.mixer, "more_cache_requests") else {}).items():
+                if name in places:
+                    raise ValueError(f"schedule call {i}: the name {name!r} is taken by a slot of the layer")
+                places[name] = take(req, (i, name))
+            more_places.append(places)
         cache = SequenceCache([(r, len(c)) for r, c in kv_groups.items()],
                               [(r, len(c)) for r, c in state_groups.items()],
                               max_tokens, self.spec.max_positions, self.rt.dtype, self.rt.device, n_slots=n_slots)
@@ -175,17 +184,27 @@ class Model:
         # A block may hand the next one its first norm half done (norm deferral, see parts/block.py): `entry`
         # is that norm's deferred form, filled by the block before; blocks without the extras run as ever.
         blocks = [self.layers[call.layer].block for call in self.spec.schedule]
+        history = None
+        if self.keeps_history:       # the stream as the embedding and every call leave it, for parts that look back over the depth
+            history = self.rt.scratch("stream_history", (len(blocks) + 1, *x.shape), torch.float32)
+            history[0].copy_(x)
         entry = None
         for i, (block, binding) in enumerate(zip(blocks, cache.bindings)):
             if self.entries[i] is not None:
                 self.entries[i].forward(x, x0, ctx)
                 entry = None                 # (the stream has changed since the block before looked at it)
             if hasattr(block, "entry_norm"):
-                nxt = getattr(blocks[i + 1], "entry_norm", None) if i + 1 < len(blocks) and self.entries[i + 1] is None else None
+                nxt = (getattr(blocks[i + 1], "entry_norm", None)
+                       if i + 1 < len(blocks) and self.entries[i + 1] is None and self.exits[i] is None else None)
                 entry = block.forward(x, ctx, binding, entry=entry, next_norm=nxt)
             else:
                 block.forward(x, ctx, binding)
                 entry = None
+            if self.exits[i] is not None:
+                self.exits[i].forward(x, history, i, ctx)
+                entry = None                 # (the stream has changed since the block looked at it)
+            elif history is not None:
+                history[i + 1].copy_(x)
             if trace is not None:
                 trace.append(x.clone())
         if trace is not None:

@@ -159,7 +159,8 @@ def lib():
                      "llmi_delta_conv_carry", "llmi_delta_recurrence", "llmi_delta_finish", "llmi_moe_route", "llmi_moe_up",
                      "llmi_moe_down", "llmi_moe_grouped", "llmi_linear_heads_mma", "llmi_attention_latent_mma", "llmi_attention_latent_mma_supported",
                      "llmi_conv_add", "llmi_conv_carry", "llmi_qkv_prepare", "llmi_attention_flex", "llmi_diff_combine",
-                     "llmi_gdelta_prepare", "llmi_dplr_recurrence", "llmi_activate", "llmi_attention_maps_mma", "llmi_attention_maps_mma_supported", "llmi_tanh_rows", "llmi_norm_conv_token"):
+                     "llmi_gdelta_prepare", "llmi_dplr_recurrence", "llmi_activate", "llmi_attention_maps_mma", "llmi_attention_maps_mma_supported", "llmi_tanh_rows", "llmi_norm_conv_token",
+                     "llmi_layernorm", "llmi_depth_mix", "llmi_gate_rows", "llmi_pool_rows"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_delta_state_floats.restype = c_long
@@ -199,8 +200,43 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
                                          eps, _stream_int()))
 
 
+def layernorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None,
+              weight2: torch.Tensor | None = None, out2: torch.Tensor | None = None) -> None:
+    """out[r] = (x[src] - mean) / sqrt(var + eps) * weight (no bias; var the mean of the squared deviations), src =
+    rows[r] if rows is given else r.  With ``weight2`` and ``out2`` a second norm of the same rows leaves in the same
+    pass (a layer whose two branches read the same x shares the row's mean and variance)."""
+    _need_cuda(x, weight, out, rows, weight2, out2)
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    n, W = out.shape
+    assert x.shape[1] == W and weight.numel() == W and (weight2 is None) == (out2 is None)
+    if out2 is not None:
+        assert out2.shape == out.shape and out2.dtype == out.dtype and out2.is_contiguous() and weight2.dtype == torch.float32
+        assert weight2.numel() == W
+    _check("layernorm", lib().llmi_layernorm(c_int(_dtype_code(out)), _ptr(x), _ptr(weight), _ptr(out), _ptr(weight2), _ptr(out2),
+                                             _ptr(rows), c_int(n), c_int(W), c_float(eps), _stream()))
+
+
+def depth_mix(x: torch.Tensor, history: torch.Tensor, n: int, coeffs: torch.Tensor) -> None:
+    """history[n] = x; then x = sum over j <= n of coeffs[j] * history[j] (j ascending, fp32).  x fp32 [T, W] contiguous;
+    history fp32 [>= n + 1, T, W] contiguous; coeffs fp32 [n + 1] on the device."""
+    _need_cuda(x, history, coeffs)
+    assert x.dtype == history.dtype == coeffs.dtype == torch.float32 and x.is_contiguous() and history.is_contiguous()
+    assert history.shape[1:] == x.shape and history.shape[0] > n and coeffs.numel() == n + 1 and coeffs.is_contiguous()
+    _check("depth_mix", lib().llmi_depth_mix(_ptr(x), _ptr(history), c_long(x.numel()), c_int(n), _ptr(coeffs), _stream()))
+
+
+def gate_rows(a: torch.Tensor, z: torch.Tensor) -> None:
+    """a[t, :] *= logistic(z[t]) in place; z fp32, one number per row (any row stride)."""
+    _need_cuda(a, z)
+    T, W = a.shape
+    assert a.stride(1) == 1 and z.dtype == torch.float32 and z.shape[0] == T
+    _check("gate_rows", lib().llmi_gate_rows(c_int(_dtype_code(a)), _ptr(a), c_long(a.stride(0)), c_int(W), _ptr(z),
+                                             c_long(z.stride(0)), c_int(T), _stream()))
+
+
 ACT_SILU, ACT_GELU_TANH = 0, 1
 ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
+EXPERT_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}      # of the routed experts' kernels (relu2: the square of relu)
 FUSED_GATE_MODES = {ACT_SILU: OUT_SWIGLU, ACT_GELU_TANH: OUT_GEGLU}     # activation -> the output mode of the products that gate in their epilogue
 
 
@@ -839,13 +875,16 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
 
 def qkv_prepare(proj: torch.Tensor, n_q_heads: int, n_k_heads: int, dk: int, n_v_heads: int, dv: int, q_norm_w, k_norm_w,
                 eps: float, inv_freq, rot_dims: int, ctx, seq_pages, page_size: int, k_cache, v_cache, q_out: torch.Tensor,
-                has_kv: bool = True, write_kv: bool = True) -> None:
+                has_kv: bool = True, write_kv: bool = True, pairing: int = 0, amplitude: float = 1.0,
+                v_from_k: bool = False) -> None:
     """From the fp32 rows [q | k | v] of a step (k, v absent without ``has_kv``): optional RMS norms over the whole q
     part and the whole k part (weights ``q_norm_w``, ``k_norm_w``), rotation of the first ``rot_dims`` entries of every
-    q and k head, q into ``q_out`` (compute type), k and v into their cache pages."""
+    q and k head (``pairing`` 0: entries (i, i + rot_dims/2); 1: neighbours (2i, 2i + 1); cos and sin times
+    ``amplitude``), q into ``q_out`` (compute type), k and v into their cache pages.  ``v_from_k``: the rows hold no v
+    part; the values are the key rows before the rotation."""
     _need_cuda(proj, q_norm_w, k_norm_w, inv_freq, seq_pages, k_cache, v_cache, q_out)
     T = proj.shape[0]
-    n_in = n_q_heads * dk + ((n_k_heads * dk + n_v_heads * dv) if has_kv else 0)
+    n_in = n_q_heads * dk + ((n_k_heads * dk + (0 if v_from_k else n_v_heads * dv)) if has_kv else 0)
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= n_in
     assert q_out.shape == (T, n_q_heads * dk) and q_out.stride(1) == 1 and seq_pages.dtype == torch.int32
     for wt, n in ((q_norm_w, n_q_heads * dk), (k_norm_w, n_k_heads * dk)):
@@ -858,6 +897,7 @@ def qkv_prepare(proj: torch.Tensor, n_q_heads: int, n_k_heads: int, dk: int, n_v
     _check("qkv_prepare", lib().llmi_qkv_prepare(
         c_int(_dtype_code(q_out)), _ptr(proj), c_long(proj.stride(0)), c_int(n_q_heads), c_int(n_k_heads), c_int(dk),
         c_int(n_v_heads), c_int(dv), _ptr(q_norm_w), _ptr(k_norm_w), c_float(eps), _ptr(inv_freq), c_int(rot_dims),
+        c_int(pairing), c_float(amplitude), c_int(1 if v_from_k else 0),
         _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(seq_pages), c_int(seq_pages.stride(0)), _ptr(seq_pages),
         c_int(seq_pages.stride(0)), c_int(page_size), _ptr(k_cache if has_kv else None), _ptr(v_cache if has_kv else None),
         _ptr(q_out), c_long(q_out.stride(0)), c_int(T), c_int(1 if has_kv else 0), c_int(1 if write_kv else 0), _stream()))
@@ -865,13 +905,23 @@ def qkv_prepare(proj: torch.Tensor, n_q_heads: int, n_k_heads: int, dk: int, n_v
 
 def attention_flex(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_pages, page_size: int, n_heads: int,
                    n_kv_heads: int, maps: int, dk: int, dv: int, scale: float, head_scale=None, window: int = 0,
-                   chunk: int = 0) -> None:
+                   chunk: int = 0, pooled=None, gate=None) -> None:
     """Causal attention of every token over its sequence's cache with ``maps`` score maps per head (query row
     [head][map][dk], key heads [kv head][map], one set of values [kv head][dv]); out [T, heads*maps*dv] in q's type or
     fp32.  ``head_scale`` fp32 [heads] multiplies the scores of a head; ``window`` and ``chunk`` limit the visible keys
-    (a query at p sees max(p - window + 1, p // chunk * chunk) .. p)."""
-    _need_cuda(q, out, k_cache, v_cache, seq_pages, head_scale)
+    (a query at p sees max(p - window + 1, p // chunk * chunk) .. p).  ``pooled`` = (pool, k_pool, v_pool, pool_pages):
+    beside its window a query sees row b of the pooled pages for every block b of ``pool`` positions that lies wholly
+    before the window (b * pool + pool - 1 <= p - window), in the same softmax.  ``gate`` fp32 [T, >= heads] (row-strided):
+    head h's output is multiplied by logistic(gate[t, h])."""
+    _need_cuda(q, out, k_cache, v_cache, seq_pages, head_scale, gate)
     T = q.shape[0]
+    pool, k_pool, v_pool, pool_pages = pooled if pooled is not None else (0, None, None, None)
+    if pool:
+        _need_cuda(k_pool, v_pool, pool_pages)
+        assert window > 0 and k_pool.dtype == v_pool.dtype == q.dtype and pool_pages.dtype == torch.int32
+        assert k_pool.shape[-3:] == (n_kv_heads * maps, page_size, dk) and v_pool.shape[-3:] == (n_kv_heads, page_size, dv)
+        assert k_pool.is_contiguous() and v_pool.is_contiguous() and pool_pages.shape[0] == seq_pages.shape[0]
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == T and gate.shape[1] >= n_heads)
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, n_heads * maps * dv) and q.shape[1] >= n_heads * maps * dk
     assert q.dtype == k_cache.dtype == v_cache.dtype and out.dtype in (q.dtype, torch.float32)
     assert k_cache.shape[-3:] == (n_kv_heads * maps, page_size, dk) and v_cache.shape[-3:] == (n_kv_heads, page_size, dv)
@@ -880,15 +930,35 @@ def attention_flex(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, se
         c_int(_dtype_code(q)), _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)),
         c_int(1 if out.dtype == torch.float32 else 0), _ptr(k_cache), _ptr(v_cache), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos),
         _ptr(seq_pages), c_int(seq_pages.stride(0)), c_int(page_size), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(maps),
-        c_int(dk), c_int(dv), c_float(scale), _ptr(head_scale), c_int(window), c_int(chunk), _stream()))
+        c_int(dk), c_int(dv), c_float(scale), _ptr(head_scale), c_int(window), c_int(chunk), c_int(pool), _ptr(k_pool), _ptr(v_pool),
+        _ptr(pool_pages), c_int(pool_pages.stride(0) if pool else 0), _ptr(gate), c_long(gate.stride(0) if gate is not None else 0),
+        _stream()))
+
+
+def pool_rows(k_cache, v_cache, seq_pages, k_pool, v_pool, pool_pages, page_size: int, pool: int, ctx) -> None:
+    """For every token of the step whose position ends a block of ``pool`` positions: the mean of the block's key rows
+    and of its value rows, as the cache holds them (added in position order in fp32), into row pos // pool of the pooled
+    pages (``k_pool``, ``v_pool`` with the page table ``pool_pages``)."""
+    _need_cuda(k_cache, v_cache, seq_pages, k_pool, v_pool, pool_pages)
+    assert k_cache.dtype == v_cache.dtype == k_pool.dtype == v_pool.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_pool.is_contiguous() and v_pool.is_contiguous() and k_pool.shape[-3:] == k_cache.shape[-3:]
+    assert v_pool.shape[-3:] == v_cache.shape[-3:] and k_cache.shape[-2] == page_size and pool >= 1
+    assert seq_pages.dtype == pool_pages.dtype == torch.int32 and seq_pages.shape[0] == pool_pages.shape[0]
+    _check("pool_rows", lib().llmi_pool_rows(
+        c_int(_dtype_code(k_cache)), _ptr(k_cache), _ptr(v_cache), _ptr(seq_pages), c_int(seq_pages.stride(0)), _ptr(k_pool),
+        _ptr(v_pool), _ptr(pool_pages), c_int(pool_pages.stride(0)), c_int(page_size), c_int(k_cache.shape[-3]),
+        c_int(k_cache.shape[-1]), c_int(v_cache.shape[-3]), c_int(v_cache.shape[-1]), c_int(pool), _ptr(ctx.tok_seq),
+        _ptr(ctx.tok_pos), c_int(ctx.tok_seq.shape[0]), _stream()))
 
 
 def attention_maps(q, out, k_cache, v_cache, ctx, seq_pages, page_size: int, n_heads: int, n_kv_heads: int, maps: int,
-                   dk: int, dv: int, scale: float, head_scale=None, window: int = 0, chunk: int = 0, rt=None) -> None:
+                   dk: int, dv: int, scale: float, head_scale=None, window: int = 0, chunk: int = 0, rt=None, pooled=None,
+                   gate=None) -> None:
     """The attention of a step in its general form (arguments as :func:`attention_flex`): bf16 sizes that the
     tensor-core kernel takes go there — prompts as blocks of 128 query rows, steps of single tokens cut over the
     positions (``rt`` lends the workspace of the cuts) —, everything else, and the 32-bit path, to the generic kernel."""
     if (q.dtype == torch.bfloat16 and rt is not None and _MAPS_ATTENTION == "mma" and not _FORCE_GENERIC_ATTENTION
+            and pooled is None and gate is None
             and lib().llmi_attention_maps_mma_supported(c_int(dk), c_int(dv), c_int(n_heads // n_kv_heads), c_int(page_size))
             and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 8 == 0):
         _need_cuda(q, out, k_cache, v_cache, seq_pages, head_scale)
@@ -911,7 +981,7 @@ def attention_maps(q, out, k_cache, v_cache, ctx, seq_pages, page_size: int, n_h
             c_int(T // 128 + S), c_int(splits), c_int(pps), _ptr(ws), c_long(n_ws), _stream()))
         return
     attention_flex(q, out, k_cache, v_cache, ctx, seq_pages, page_size, n_heads, n_kv_heads, maps, dk, dv, scale, head_scale,
-                   window, chunk)
+                   window, chunk, pooled, gate)
 
 
 _MAPS_ATTENTION = os.environ.get("LLMI_MAPS_ATTENTION", "mma")      # "generic": the fp32-arithmetic kernel for everything
@@ -1240,26 +1310,38 @@ def dplr_recurrence(proj: torch.Tensor, prep: torch.Tensor, H: int, D: int, Dv: 
 # ---------------------------------------------------------------------------------------------
 # Routed experts
 
-def moe_route(logits: torch.Tensor, top: int, ctx, idx: torch.Tensor, wt: torch.Tensor) -> None:
+ROUTE_SOFTMAX_CHOSEN, ROUTE_LOGISTIC_NORMALISED = 0, 1
+ROUTE_MODES = {"softmax_chosen": ROUTE_SOFTMAX_CHOSEN, "logistic_normalised": ROUTE_LOGISTIC_NORMALISED}
+
+
+def moe_route(logits: torch.Tensor, top: int, ctx, idx: torch.Tensor, wt: torch.Tensor, mode: int = ROUTE_SOFTMAX_CHOSEN,
+              n_groups: int = 0, keep: int = 0, experts: int | None = None) -> None:
     """The ``top`` largest of each row's fp32 logits (ties: the lower index) into ``idx`` int32 [T, top], and the
-    softmax over them into ``wt`` fp32 [T, top]; a token row of no sequence gets index -1."""
+    softmax over them into ``wt`` fp32 [T, top]; a token row of no sequence gets index -1.  ``mode``
+    ROUTE_LOGISTIC_NORMALISED: the scores are logistic(logit) and the weights the chosen scores over their sum (+ 1e-20).
+    ``n_groups`` > 1 with ``keep`` < n_groups: only experts of the ``keep`` best of ``n_groups`` equal runs of neighbours
+    can be chosen (a run's score: the sum of its two largest scores).  ``experts``: the first columns of ``logits`` that
+    are experts (default: all)."""
     _need_cuda(logits, idx, wt)
     T, E = logits.shape
+    E = E if experts is None else int(experts)
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and idx.dtype == torch.int32 and wt.dtype == torch.float32
     assert idx.shape == (T, top) and wt.shape == (T, top) and idx.is_contiguous() and wt.is_contiguous()
-    _check("moe_route", lib().llmi_moe_route(_ptr(logits), c_long(logits.stride(0)), c_int(E), c_int(top), _ptr(ctx.tok_seq),
-                                             _ptr(idx), _ptr(wt), c_int(T), _stream()))
+    _check("moe_route", lib().llmi_moe_route(_ptr(logits), c_long(logits.stride(0)), c_int(E), c_int(top), c_int(mode),
+                                             c_int(n_groups), c_int(keep), _ptr(ctx.tok_seq), _ptr(idx), _ptr(wt), c_int(T),
+                                             _stream()))
 
 
 def moe_experts_streamed(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int, a: torch.Tensor, y: torch.Tensor) -> None:
     """y = sum over each token's choices of wt * down_e(act(gate_e h) * up_e h); the weight-streaming form.
-    w_gate, w_up [E, F, W], w_down [E, W, F] in h's type; a fp32 [T, top, F] scratch; y fp32 [T, W] (stored)."""
+    w_gate, w_up [E, F, W], w_down [E, W, F] in h's type; a fp32 [T, top, F] scratch; y fp32 [T, W] (stored).
+    ``w_gate`` None: experts without a gate matrix, down_e(act(up_e h))."""
     _need_cuda(h, w_gate, w_up, w_down, idx, wt, a, y)
     T, W = h.shape
-    E, F, _ = w_gate.shape
+    E, F, _ = w_up.shape
     top = idx.shape[1]
-    assert h.stride(1) == 1 and h.dtype == w_gate.dtype == w_up.dtype == w_down.dtype
-    assert w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous() and w_down.shape == (E, W, F)
+    assert h.stride(1) == 1 and h.dtype == w_up.dtype == w_down.dtype and (w_gate is None or w_gate.dtype == h.dtype)
+    assert (w_gate is None or (w_gate.is_contiguous() and w_gate.shape == w_up.shape)) and w_up.is_contiguous() and w_down.is_contiguous() and w_down.shape == (E, W, F)
     assert a.dtype == torch.float32 and a.is_contiguous() and a.numel() >= T * top * F and y.dtype == torch.float32 and y.stride(1) == 1
     l = lib()
     _check("moe_up", l.llmi_moe_up(c_int(_dtype_code(h)), _ptr(h), c_long(h.stride(0)), _ptr(w_gate), _ptr(w_up), c_int(W), c_int(F),
@@ -1282,10 +1364,10 @@ def moe_experts_grouped(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int
     and each expert's products run as tensor-core tiles over its rows.  bf16; ``rt`` lends the scratch."""
     _need_cuda(h, w_gate, w_up, w_down, idx, wt, y)
     T, W = h.shape
-    E, F, _ = w_gate.shape
+    E, F, _ = w_up.shape
     top = idx.shape[1]
-    assert h.dtype == w_gate.dtype == w_up.dtype == w_down.dtype == torch.bfloat16 and h.stride(1) == 1
-    assert w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous() and w_down.shape == (E, W, F)
+    assert h.dtype == w_up.dtype == w_down.dtype == torch.bfloat16 and h.stride(1) == 1
+    assert (w_gate is None or (w_gate.dtype == torch.bfloat16 and w_gate.is_contiguous() and w_gate.shape == w_up.shape)) and w_up.is_contiguous() and w_down.is_contiguous() and w_down.shape == (E, W, F)
     assert y.dtype == torch.float32 and y.stride(1) == 1 and idx.is_contiguous() and wt.is_contiguous()
     n_int = int(lib().llmi_moe_group_ints(c_int(T * top), c_int(E)))
     scratch = rt.scratch("experts_groups", (n_int,), torch.int32)

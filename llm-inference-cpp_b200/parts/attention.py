@@ -251,3 +251,97 @@ class QKNormedAttention(_MapsAttention):
         return self._project_out(self._attend(h, ctx, binding), x, store, then_norm)
 
     stores_output = True
+
+
+@part("mixer", "window_pool_attention")
+class WindowPoolAttention(_MapsAttention):
+    """Attention over a sliding window and, beside it, over one pooled key and value per block of positions that has
+    left the window — optional pieces, each a parameter:
+
+    * ``window`` (0: every earlier position) and ``pool`` (0: nothing beyond the window): the query at position p sees
+      the positions j with 0 <= p - j < window and, for every block b of ``pool`` positions with b*pool + pool - 1 <=
+      p - window, ONE key and ONE value: the means of the block's keys and values as the cache holds them (keys after
+      the rotation).  Positions that have left the window and whose block is not complete before it are not seen.  All
+      visible keys share one softmax.  The pooled rows live in cache pages of their own, one row per block
+      (``more_cache_requests``), and are made when a block's last position arrives; the token pages are a windowed
+      group, so pages that lie wholly before the window (and before the newest block) go back to the pool early.
+    * ``values_from_keys``: there is no value projection; the values are the keys as projected, before the rotation.
+    * ``gate``: head h's output is multiplied by logistic(W_g h)_h, one number per head from the mixer's input, before
+      the output projection.
+    * ``position``: a PartSpec of the position family whose ``inv_freq``, ``rotary_dim``, ``pairing`` and ``amplitude``
+      the preparation kernel applies to q and k.
+
+    params: ``width``, ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``window``, ``pool``, ``values_from_keys``,
+    ``gate``, ``position``.  tensors: ``q`` [heads*dim, width], ``k`` [kv_heads*dim, width], ``v`` [kv_heads*vdim, width]
+    (absent with ``values_from_keys``), ``g`` [heads, width] (with ``gate``), ``o`` [width, heads*vdim]."""
+
+    @classmethod
+    def declare(cls, spec):
+        p = spec.params
+        d = cls._declare_projections(p, 1)
+        if p.get("values_from_keys", False):
+            del d["v"]
+        if p.get("gate", False):
+            d["g"] = TensorDecl((p["heads"], p["width"]))
+        d.update(nested_declare("position", p["position"]))
+        return d
+
+    def __init__(self, spec, tensors, rt, **_):
+        p = dict(spec.params)
+        p.setdefault("eps", 0.0)
+        self.rt = rt
+        self._sizes(p)
+        self.pool = int(p.get("pool", 0))
+        self.values_from_keys = bool(p.get("values_from_keys", False))
+        self.gated = bool(p.get("gate", False))
+        if self.pool and not self.window:
+            raise ValueError("window_pool_attention: pooled blocks lie before a window; without a window there are none")
+        if self.values_from_keys and self.Dv != self.D:
+            raise ValueError("window_pool_attention: values that are the keys have the keys' size")
+        names = ["q", "k"] + ([] if self.values_from_keys else ["v"]) + (["g"] if self.gated else [])
+        self.w_in = rt.to_compute(torch.cat([tensors[n] for n in names], dim=0))      # one product: [q | k | (v) | (gate)]
+        self.w_o = rt.to_compute(tensors["o"])
+        self.n_qkv = self.H * self.D + self.G * self.D + (0 if self.values_from_keys else self.G * self.Dv)
+        self.position = nested_build("position", p["position"], tensors, rt)
+        self.inv_freq, self.rot_dims = self.position.inv_freq, int(self.position.rotary_dim)
+        if self.rot_dims > self.D:
+            raise ValueError("window_pool_attention: the rotated part is larger than a head")
+
+    def cache_request(self):
+        # the newest block's positions must still be there when its last one arrives: the window of the pages is the
+        # larger of the two
+        window = max(self.window, self.pool) if self.window else 0
+        return KVRequest(self.G, self.D, window, True, self.G, self.Dv)
+
+    def more_cache_requests(self):
+        if not self.pool:
+            return {}
+        return {"pooled": KVRequest(self.G, self.D, 0, True, self.G, self.Dv, every=self.pool)}
+
+    def forward(self, h, x, ctx, binding, store: bool = False, then_norm=None) -> bool:
+        T = h.shape[0]
+        rt, H, G, D, Dv = self.rt, self.H, self.G, self.D, self.Dv
+        proj = rt.scratch("attn_proj", (T, self.w_in.shape[0]), torch.float32)
+        kernels.linear(h, self.w_in, proj, None, kernels.OUT_STORE_F32)
+        g = binding.group
+        pages = ctx.pages_of(g)
+        k_cache, v_cache = g.k[binding.index], g.v[binding.index]
+        q = rt.scratch("attn_q", (T, H * D))
+        kernels.qkv_prepare(proj, H, G, D, G, Dv, None, None, 0.0, self.inv_freq, self.rot_dims, ctx, pages, g.page_size,
+                            k_cache, v_cache, q, has_kv=True, write_kv=binding.writes, pairing=self.position.pairing,
+                            amplitude=float(self.position.amplitude), v_from_k=self.values_from_keys)
+        pooled = None
+        if self.pool:
+            pb = binding.more["pooled"]
+            pg = pb.group
+            k_pool, v_pool, pool_pages = pg.k[pb.index], pg.v[pb.index], ctx.pages_of(pg)
+            if binding.writes:
+                kernels.pool_rows(k_cache, v_cache, pages, k_pool, v_pool, pool_pages, g.page_size, self.pool, ctx)
+            pooled = (self.pool, k_pool, v_pool, pool_pages)
+        gate = proj[:, self.n_qkv:] if self.gated else None
+        out = rt.scratch("attn_out", (T, H * Dv))
+        kernels.attention_maps(q, out, k_cache, v_cache, ctx, pages, g.page_size, H, G, 1, D, Dv, self.scale, None,
+                               self.window, 0, rt=rt, pooled=pooled, gate=gate)
+        return self._project_out(out, x, store, then_norm)
+
+    stores_output = True

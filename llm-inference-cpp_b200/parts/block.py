@@ -70,6 +70,33 @@ class PreNormBlock:
         return None
 
 
+@part("block", "parallel")
+class ParallelBlock:
+    """Both sublayers read the SAME x, each through a norm of its own, and are added at once:
+    x += mixer(norm1(x)) + ffn(norm2(x)).  The feed-forward (with its norm) may be absent.  Both norms are computed
+    before either sublayer touches x — in one pass over x where the norms offer ``forward_pair``."""
+
+    def __init__(self, mixer_norm, mixer, ffn_norm=None, ffn=None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("parallel: a feed-forward comes with its norm, or not at all")
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
+
+    @property
+    def takes_padding_rows(self) -> bool:
+        return True          # rows are treated alone
+
+    def forward(self, x, ctx, binding):
+        if self.ffn is None:
+            self.mixer.forward(self.mixer_norm.forward(x), x, ctx, binding)
+            return
+        pair = self.mixer_norm.forward_pair(self.ffn_norm, x) if hasattr(self.mixer_norm, "forward_pair") else None
+        if pair is None:
+            pair = (self.mixer_norm.forward(x, scratch_name="norm_out"), self.ffn_norm.forward(x, scratch_name="norm_out_b"))
+        h1, h2 = pair
+        self.mixer.forward(h1, x, ctx, binding)
+        self.ffn.forward(h2, x, ctx)
+
+
 @part("block", "prepost")
 class PrePostNormBlock:
     """A norm ahead of AND behind each sublayer:  x += post1(mixer(pre1(x)));  x += post2(ffn(pre2(x))).

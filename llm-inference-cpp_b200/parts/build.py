@@ -7,7 +7,7 @@ the parts appear.
 """
 from __future__ import annotations
 
-from . import attention, block, conv, delta, embedding, experts, feedforward, latent, loop, norm, position  # noqa: F401  (register the built-in parts)
+from . import attention, block, conv, delta, depth, embedding, experts, feedforward, latent, loop, norm, position  # noqa: F401  (register the built-in parts)
 from .registry import TensorDecl, get_part
 from .spec import ModelSpec, PartSpec
 
@@ -20,6 +20,8 @@ def _part_specs(spec: ModelSpec):
     for call in spec.schedule:
         if call.before is not None:
             yield "pass_entry", call.before
+        if call.after is not None:
+            yield "pass_exit", call.after
     yield "norm", spec.final_norm
     yield "head", spec.head
 
@@ -76,3 +78,8 @@ def build_parts(spec: ModelSpec, tensors: dict, rt):
 def build_entries(spec: ModelSpec, tensors: dict, rt) -> list:
     """The ``pass_entry`` part of every scheduled call (None where a call has none), in schedule order."""
     return [None if call.before is None else _make("pass_entry", call.before, tensors, rt) for call in spec.schedule]
+
+
+def build_exits(spec: ModelSpec, tensors: dict, rt) -> list:
+    """The ``pass_exit`` part of every scheduled call (None where a call has none), in schedule order."""
+    return [None if call.after is None else _make("pass_exit", call.after, tensors, rt) for call in spec.schedule]

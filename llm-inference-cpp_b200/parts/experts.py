@@ -1,8 +1,14 @@
-"""Feed-forward ``routed_experts``: a mixture of small gated feed-forwards of which every token runs a few.
+"""Feed-forward ``routed_experts``: a mixture of small feed-forwards of which every token runs a few.
 
 Router logits z = W_r h in fp32; the ``top`` experts with the largest logits are chosen (ties: the lower index) and
 weighted by the softmax over the CHOSEN logits only; the output is the weighted sum of the chosen experts' outputs,
 each W_down (act(W_gate h) * (W_up h)) without biases, summed in the order of the choice.
+
+Variations, each a parameter: ``scoring`` ``logistic_normalised`` — scores s = logistic(z), the ``top`` largest scores
+are chosen and weighted by s / (sum of the chosen s + 1e-20); ``groups`` = (count, keep) — the experts form ``count``
+equal runs of neighbours, a run's score is the sum of its two largest scores, and only experts of the ``keep`` best runs
+can be chosen; ``gated`` False — experts without a gate matrix, W_down act(W_up h); ``shared`` — one more expert of the
+same form (inner size ``shared``) that every token runs, added times logistic(W_sg h), one number per token.
 """
 from __future__ import annotations
 
@@ -14,9 +20,12 @@ from .registry import TensorDecl, part
 
 @part("ffn", "routed_experts")
 class RoutedExperts:
-    """params: ``width``, ``inner`` (of one expert), ``experts``, ``top``, optional ``activation`` (default ``silu``).
-    tensors: ``router`` [experts, width] and per expert i ``e<i>.gate``, ``e<i>.up`` [inner, width], ``e<i>.down``
-    [width, inner]."""
+    """params: ``width``, ``inner`` (of one expert), ``experts``, ``top``, optional ``activation`` (``silu``,
+    ``gelu_tanh``, ``relu2``; default ``silu``), ``gated`` (default True), ``scoring`` (``softmax_chosen``,
+    ``logistic_normalised``), ``groups`` ((count, keep) or None), ``shared`` (inner size of the shared expert; 0: none).
+    tensors: ``router`` [experts, width] and per expert i ``e<i>.gate`` (if gated), ``e<i>.up`` [inner, width],
+    ``e<i>.down`` [width, inner]; with a shared expert ``shared.up`` [shared, width], ``shared.down`` [width, shared]
+    and ``shared.sg`` [1, width]."""
     takes_padding_rows = True       # the router marks token rows of no sequence; they get zeros
     stores_output = True
 
@@ -26,8 +35,13 @@ class RoutedExperts:
         W, F = p["width"], p["inner"]
         d = {}
         for i in range(p["experts"]):
-            d.update({f"e{i}.gate": TensorDecl((F, W)), f"e{i}.up": TensorDecl((F, W)), f"e{i}.down": TensorDecl((W, F))})
+            if p.get("gated", True):
+                d[f"e{i}.gate"] = TensorDecl((F, W))
+            d.update({f"e{i}.up": TensorDecl((F, W)), f"e{i}.down": TensorDecl((W, F))})
         d["router"] = TensorDecl((p["experts"], W))
+        if p.get("shared", 0):
+            S = p["shared"]
+            d.update({"shared.up": TensorDecl((S, W)), "shared.down": TensorDecl((W, S)), "shared.sg": TensorDecl((1, W))})
         return d
 
     def __init__(self, spec, tensors, rt, **_):
@@ -37,25 +51,44 @@ class RoutedExperts:
         if not (1 <= self.top <= self.E):
             raise ValueError("routed_experts: top must be between 1 and the number of experts")
         activation = p.get("activation", "silu")
-        if activation not in kernels.ACTIVATIONS:
+        if activation not in kernels.EXPERT_ACTIVATIONS:
             raise ValueError(f"routed_experts: unknown activation {activation!r}")
-        self.act = kernels.ACTIVATIONS[activation]
-        self.w_router = rt.to_compute(tensors["router"])
-        self.w_gate = rt.to_compute(torch.stack([tensors[f"e{i}.gate"] for i in range(self.E)]))
+        self.act = kernels.EXPERT_ACTIVATIONS[activation]
+        self.gated = bool(p.get("gated", True))
+        if self.gated == (activation == "relu2"):
+            raise ValueError("routed_experts: gated experts take silu or gelu_tanh, experts without a gate relu2")
+        scoring = p.get("scoring", "softmax_chosen")
+        if scoring not in kernels.ROUTE_MODES:
+            raise ValueError(f"routed_experts: unknown scoring {scoring!r} (known: {sorted(kernels.ROUTE_MODES)})")
+        self.route_mode = kernels.ROUTE_MODES[scoring]
+        self.n_groups, self.keep = (int(v) for v in (p.get("groups") or (0, 0)))
+        if self.n_groups and (self.E % self.n_groups or not (1 <= self.keep <= self.n_groups)
+                              or self.keep * (self.E // self.n_groups) < self.top):
+            raise ValueError("routed_experts: the groups must divide the experts, and the kept ones hold at least `top` experts")
+        self.shared = int(p.get("shared", 0))
+        router = tensors["router"]
+        if self.shared:      # the shared expert's gate rides on the router's product: one more row of logits
+            router = torch.cat([router, tensors["shared.sg"].reshape(1, self.width)], dim=0)
+            self.w_shared_up, self.w_shared_down = rt.to_compute(tensors["shared.up"]), rt.to_compute(tensors["shared.down"])
+        self.w_router = rt.to_compute(router)
+        self.w_gate = rt.to_compute(torch.stack([tensors[f"e{i}.gate"] for i in range(self.E)])) if self.gated else None
         self.w_up = rt.to_compute(torch.stack([tensors[f"e{i}.up"] for i in range(self.E)]))
         self.w_down = rt.to_compute(torch.stack([tensors[f"e{i}.down"] for i in range(self.E)]))
 
     def weight_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in (self.w_router, self.w_gate, self.w_up, self.w_down))
+        ws = [self.w_router, self.w_up, self.w_down] + ([self.w_gate] if self.gated else [])
+        if self.shared:
+            ws += [self.w_shared_up, self.w_shared_down]
+        return sum(t.numel() * t.element_size() for t in ws)
 
     def forward(self, h, x, ctx, store: bool = False) -> bool:
         T = h.shape[0]
         rt = self.rt
-        logits = rt.scratch("router_logits", (T, self.E), torch.float32)
+        logits = rt.scratch("router_logits", (T, self.w_router.shape[0]), torch.float32)
         kernels.linear(h, self.w_router, logits, None, kernels.OUT_STORE_F32)
         idx = rt.scratch("router_choice", (T, self.top), torch.int32)
         wt = rt.scratch("router_weight", (T, self.top), torch.float32)
-        kernels.moe_route(logits, self.top, ctx, idx, wt)
+        kernels.moe_route(logits, self.top, ctx, idx, wt, self.route_mode, self.n_groups, self.keep, experts=self.E)
         y = x if store else rt.scratch("experts_out", tuple(x.shape), torch.float32)
         if kernels.moe_grouped_applies(h, self.width, self.inner, self.E):
             kernels.moe_experts_grouped(h, self.w_gate, self.w_up, self.w_down, idx, wt, self.act, rt, y)
@@ -64,4 +97,9 @@ class RoutedExperts:
             kernels.moe_experts_streamed(h, self.w_gate, self.w_up, self.w_down, idx, wt, self.act, a, y)
         if not store:
             x += y
+        if self.shared:      # every token's expert: x += logistic(z_sg) * W_down act(W_up h); the gate scales the activation rows
+            sa = rt.scratch("shared_act", (T, self.shared))
+            kernels.linear(h, self.w_shared_up, sa, None, kernels.OUT_RELU2)
+            kernels.gate_rows(sa, logits[:, self.E:])
+            kernels.linear(sa, self.w_shared_down, x, None, kernels.OUT_ADD_F32)
         return False

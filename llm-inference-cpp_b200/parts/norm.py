@@ -43,6 +43,40 @@ class RMSNorm:
         return kernels.DeferredNorm(self.weight, self.eps, h, ss)
 
 
+@part("norm", "layernorm")
+class LayerNorm:
+    """y = (x - mean) / sqrt(var + eps) * weight: a layer norm with a weight and no bias; var is the mean of the squared
+    deviations, all sums in fp32.  params: ``width``, ``eps``, optional ``tensor`` (the weight's local name; default
+    ``weight``).  Two norms of this kind that read the same rows can leave in one pass (:meth:`forward_pair`)."""
+    takes_padding_rows = True       # rows are treated alone
+
+    @classmethod
+    def declare(cls, spec):
+        return {spec.params.get("tensor", "weight"): TensorDecl((spec.params["width"],), "norm_scale")}
+
+    def __init__(self, spec, tensors, rt, **_):
+        self.width = int(spec.params["width"])
+        self.eps = float(spec.params["eps"])
+        self.weight = rt.to_f32(tensors[spec.params.get("tensor", "weight")])
+        self.rt = rt
+
+    def forward(self, x, rows=None, scratch_name: str = "norm_out"):
+        """x fp32 [tokens, width] -> normalised rows in the compute type; ``rows`` picks input rows."""
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = self.rt.scratch(scratch_name, (n, self.width))
+        kernels.layernorm(x, self.weight, out, self.eps, rows)
+        return out
+
+    def forward_pair(self, other, x, scratch_names=("norm_out", "norm_out_b")):
+        """(self(x), other(x)) from one read of x, or None if ``other`` is no norm of this kind with the same eps."""
+        if type(other) is not LayerNorm or other.eps != self.eps or other.width != self.width:
+            return None
+        a = self.rt.scratch(scratch_names[0], (x.shape[0], self.width))
+        b = self.rt.scratch(scratch_names[1], (x.shape[0], self.width))
+        kernels.layernorm(x, self.weight, a, self.eps, None, other.weight, b)
+        return a, b
+
+
 @part("norm", "dyt")
 class DynamicTanh:
     """Dynamic Tanh: y = tanh(alpha * x) * weight + bias — a norm without statistics.  params: ``width``.

@@ -11,7 +11,8 @@ Families and what the engine calls on their members (``rt`` is the
                ``rotate_and_store(qkv, ctx, binding, n_heads, n_kv_heads, head_dim)``, or by the
                embedding, which calls ``at_embedding(x, ctx)`` after the lookup (may add to ``x``)
 ``mixer``      ``cache_request() -> KVRequest | StateRequest | None`` and
-               ``forward(h, x, ctx, binding)``: adds its output to ``x``
+               ``forward(h, x, ctx, binding)``: adds its output to ``x``; optionally ``more_cache_requests() -> {name:
+               request}`` for what it keeps beside that (handed to it as ``binding.more[name]``)
 ``ffn``        ``forward(h, x, ctx)``: adds its output to ``x``
 ``block``      ``forward(x, ctx, binding)``: one layer's arrangement of the above; built with one keyword argument
                per filled slot of its ``LayerSpec`` (``mixer_norm``, ``mixer``, ``ffn_norm``, ``ffn`` and whatever
@@ -20,6 +21,10 @@ Families and what the engine calls on their members (``rt`` is the
 ``head``       ``forward(h_rows) -> logits fp32 [rows, vocab]``
 ``pass_entry`` ``forward(x, x0, ctx)``: acts on the stream right before a scheduled call (``ScheduleEntry.before``); ``x0`` is
                the embedding output, kept for the step if the part sets ``needs_embedding_output``
+``pass_exit``  ``forward(x, history, index, ctx)``: acts on the stream right behind scheduled call ``index``
+               (``ScheduleEntry.after``); ``history`` fp32 ``[calls + 1, tokens, width]`` is the model's record of the
+               step: row 0 the embedding output, row j + 1 the result of call j.  The part files the result of its call
+               (``history[index + 1] = x``) and may then rewrite ``x`` from the rows so far
 ``conv``       ``cache_request() -> StateRequest | None`` and ``forward(h, ctx, binding) -> h'``: reshapes a sublayer's input
                over time (a short causal convolution) and keeps the inputs it still needs per sequence; ``binding`` is
                its own place in the cache (``CacheBinding.more[slot]`` of the call).  Any part of a layer other than the
@@ -53,7 +58,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-FAMILIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head", "pass_entry", "conv")
+FAMILIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head", "pass_entry", "conv", "pass_exit")
 _PARTS: dict[str, dict[str, type]] = {f: {} for f in FAMILIES}
 
 
@@ -72,7 +77,7 @@ def resolved_shape(shape) -> tuple:
 @dataclass(frozen=True)
 class TensorDecl:
     shape: tuple                    # sizes; an entry may be a FreeDim
-    # "matrix" | "norm_scale" | "bias" | "table": floating tensors (the role says how random weights draw them);
+    # "matrix" | "norm_scale" | "bias" | "table" | "mix": floating tensors (the role says how random weights draw them);
     # "int_table": the only role a file may store as integers
     role: str = "matrix"
 

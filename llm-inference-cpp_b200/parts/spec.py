@@ -55,11 +55,14 @@ class ScheduleEntry:
     of keeping one of its own (None: its own).  A call that reads another call's
     cache writes nothing into it.  ``before`` is a part of the family ``pass_entry``
     that acts on the stream right before this call (what a pass over a looped span
-    of layers adds ahead of its first layer).
+    of layers adds ahead of its first layer).  ``after`` is a part of the family ``pass_exit`` that acts on the
+    stream right behind this call and may look at the stream as every earlier call left it (a learned mixture over
+    the depth of the model).
     """
     layer: int
     cache_of: Optional[int] = None
     before: Optional[PartSpec] = None
+    after: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
