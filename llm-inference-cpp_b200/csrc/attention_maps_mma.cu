@@ -18,6 +18,10 @@
 //                  the four states meet in shared memory in warp order, and the block leaves (maximum, sum,
 //                  unnormalised O) per row in a workspace, one part per cut, which a second kernel joins in a fixed
 //                  order — or the finished row, when the positions are not cut.
+// Optionally (pool > 0, beside a window) a query also sees one pooled key and value per block of `pool` positions that
+// lies wholly before its window: rows of pages of their own (one row per block), walked as further 64-row tiles AHEAD of
+// the window's pages in the same loop and the same running softmax; and optionally every head's output is multiplied by
+// the logistic function of a number per (token, head).
 // The order of every addition depends on positions only (pages anchored at multiples of 64, parts by key index), not
 // on the batch; cuts follow the page table's width, which is part of a recorded step's shape.
 #include <math.h>
@@ -56,7 +60,21 @@ struct MapsArgs {
   int splits, pages_per_split;  // single tokens
   float* ws_o;                  // [T * H * maps][splits][dv]
   float* ws_ml;                 // [T * H * maps][splits][2]
+  int pool;                     // positions per pooled block (0: none)
+  const __nv_bfloat16* k_pool;  // [page][kv_heads * maps][64][dk], one row per block
+  const __nv_bfloat16* v_pool;  // [page][kv_heads][64][dv]
+  const int32_t* pool_pages;    // [n_seqs, pool_pages_stride]
+  int pool_pages_stride;
+  const float* gate;            // [T, ldg]: head h's output times logistic(gate[t * ldg + h]); null: none
+  long ldg;
 };
+
+__device__ __forceinline__ int maps_pooled_visible(int pos, int window, int pool) {
+  return (pool > 0 && window > 0 && pos - window + 1 > 0) ? (pos - window + 1) / pool : 0;
+}
+__device__ __forceinline__ float maps_gate(const MapsArgs& a, int t, int head) {
+  return a.gate ? 1.0f / (1.0f + __expf(-a.gate[(size_t)t * a.ldg + head])) : 1.0f;
+}
 
 // NV = dv / 16.  PROMPT: the form (see above).
 template <int NV, bool PROMPT>
@@ -127,8 +145,8 @@ attention_maps_mma_kernel(const MapsArgs a) {
     *reinterpret_cast<uint4*>(q_s + r * ldk + 8 * c8) = v;
   }
 
-  // my two rows (g and g + 8 of my warp's 16): position, first visible key, factor on the scores
-  int row_pos[2], row_lo[2];
+  // my two rows (g and g + 8 of my warp's 16): position, first visible key, pooled blocks it sees, factor on the scores
+  int row_pos[2], row_lo[2], row_nb[2];
   float row_scale[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -136,6 +154,7 @@ attention_maps_mma_kernel(const MapsArgs a) {
     const bool ok = PROMPT ? r < n_rows : r < group;
     row_pos[i] = ok ? (PROMPT ? p_first + r : p_first) : -1;
     row_lo[i] = ok ? first_visible(row_pos[i], a.window, a.chunk) : 0;
+    row_nb[i] = ok ? maps_pooled_visible(row_pos[i], a.window, a.pool) : 0;
     const int head = PROMPT ? head0 : head0 + (ok ? r : 0);
     row_scale[i] = a.head_scale ? a.scale_log2 * a.head_scale[head] : a.scale_log2;
   }
@@ -150,7 +169,13 @@ attention_maps_mma_kernel(const MapsArgs a) {
     w_lo = lo_first;
   }
 
-  int pg_lo = lo_first / AM_PAGE, pg_hi = p_last / AM_PAGE;
+  // The tiles the block walks, numbered from 0: first the pooled pages that its rows see (n_pp of them), then the
+  // window's pages tpg_lo ..; `pg` below is this number.
+  const int w_nb = maps_pooled_visible(w_hi, a.window, a.pool);            // pooled blocks my warp's rows see at most
+  const int n_pool_rows = a.pool > 0 ? (newest + 1) / a.pool : 0;          // pooled rows the sequence holds
+  const int n_pp = (maps_pooled_visible(p_last, a.window, a.pool) + AM_PAGE - 1) / AM_PAGE;
+  const int tpg_lo = lo_first / AM_PAGE;
+  int pg_lo = 0, pg_hi = n_pp + (p_last / AM_PAGE - tpg_lo);
   if (!PROMPT) {
     pg_lo += split * a.pages_per_split;
     pg_hi = min(pg_hi, pg_lo + a.pages_per_split - 1);
@@ -160,14 +185,19 @@ attention_maps_mma_kernel(const MapsArgs a) {
   // my first 16-byte piece of a key tile and the step from one of my pieces to the next (no division per piece)
   const int kr0 = threadIdx.x / chunks_k, kc0 = threadIdx.x - kr0 * chunks_k;
   const int kr_step = blockDim.x / chunks_k, kc_step = blockDim.x - kr_step * chunks_k;
-  auto page_of = [&](int pg) { return pg <= pg_hi ? a.seq_pages[(size_t)seq * a.pages_stride + pg] : -1; };
+  auto page_of = [&](int pg) {
+    if (pg > pg_hi) return -1;
+    return pg < n_pp ? a.pool_pages[(size_t)seq * a.pool_pages_stride + pg] : a.seq_pages[(size_t)seq * a.pages_stride + tpg_lo + pg - n_pp];
+  };
   // `page`: the page's index in the cache, read from the table one iteration ahead of its copies
   auto fetch = [&](int pg, int buf, int page) {
-    const __nv_bfloat16* ksrc = a.k_cache + ((size_t)(page < 0 ? 0 : page) * (a.G * a.maps) + kh) * AM_PAGE * dk;
-    const __nv_bfloat16* vsrc = a.v_cache + ((size_t)(page < 0 ? 0 : page) * a.G + kvh) * AM_PAGE * DV;
+    const bool pooled = pg < n_pp;
+    const __nv_bfloat16* ksrc = (pooled ? a.k_pool : a.k_cache) + ((size_t)(page < 0 ? 0 : page) * (a.G * a.maps) + kh) * AM_PAGE * dk;
+    const __nv_bfloat16* vsrc = (pooled ? a.v_pool : a.v_cache) + ((size_t)(page < 0 ? 0 : page) * a.G + kvh) * AM_PAGE * DV;
     __nv_bfloat16* kd = k_s + (size_t)buf * AM_PAGE * ldk;
     __nv_bfloat16* vd = v_s + (size_t)buf * AM_PAGE * ldv;
-    const int live_rows = page < 0 ? 0 : newest - pg * AM_PAGE + 1;      // rows of the page that hold a position
+    // rows of the page that hold a position (or a finished block)
+    const int live_rows = page < 0 ? 0 : pooled ? n_pool_rows - pg * AM_PAGE : newest - (tpg_lo + pg - n_pp) * AM_PAGE + 1;
     for (int r = kr0, c8 = kc0; r < AM_PAGE;) {
       const bool live = r < live_rows;
       cp_async16(kd + r * ldk + 8 * c8, live ? ksrc + (size_t)r * dk + 8 * c8 : a.k_cache, live ? 16 : 0);
@@ -205,8 +235,9 @@ attention_maps_mma_kernel(const MapsArgs a) {
     if (pg + NBUF - 1 <= pg_hi) fetch(pg + NBUF - 1, (pg - pg_lo + NBUF - 1) % NBUF, page_next);
     else cp_async_commit();
     page_next = page_of(pg + NBUF);
-    const int base = pg * AM_PAGE + key_off;
-    if (base > w_hi || base + 16 * NT2 - 1 < w_lo) continue;     // nothing here for my rows
+    const bool pooled = pg < n_pp;
+    const int base = (pooled ? pg : tpg_lo + pg - n_pp) * AM_PAGE + key_off;     // the first of my keys: a block's or a position's index
+    if (pooled ? base >= w_nb : (base > w_hi || base + 16 * NT2 - 1 < w_lo)) continue;     // nothing here for my rows
     const __nv_bfloat16* kt = k_s + (size_t)buf * AM_PAGE * ldk;
     const __nv_bfloat16* vt = v_s + (size_t)buf * AM_PAGE * ldv;
 
@@ -234,7 +265,8 @@ attention_maps_mma_kernel(const MapsArgs a) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = base + 8 * j + 2 * tq + (e & 1), i = e >> 1;
-        const float v = (key <= row_pos[i] && key >= row_lo[i]) ? s[j][e] * row_scale[i] : -INFINITY;
+        const bool seen = pooled ? key < row_nb[i] : (key <= row_pos[i] && key >= row_lo[i]);
+        const float v = seen ? s[j][e] * row_scale[i] : -INFINITY;
         s[j][e] = v;
         mx[i] = fmaxf(mx[i], v);
       }
@@ -289,7 +321,7 @@ attention_maps_mma_kernel(const MapsArgs a) {
     if (!PROMPT || row_pos[i] < 0) continue;
     {
       const int t = t0 + 16 * warp + g + 8 * i;
-      const float inv = 1.0f / l_run[i];
+      const float inv = maps_gate(a, t, head0) / l_run[i];
       const size_t at = (size_t)t * a.ldo + (size_t)(head0 * a.maps + mp) * DV + 2 * tq;
 #pragma unroll
       for (int j = 0; j < 2 * NV; ++j) {
@@ -331,8 +363,9 @@ attention_maps_mma_kernel(const MapsArgs a) {
       const size_t hm = (size_t)(head0 + r) * a.maps + mp;
       if (a.splits == 1) {
         const size_t at = (size_t)t0 * a.ldo + hm * DV + c;
-        if (a.out_f32) ((float*)a.out)[at] = acc / l;
-        else ((__nv_bfloat16*)a.out)[at] = __float2bfloat16_rn(acc / l);
+        const float res = acc / l * maps_gate(a, t0, head0 + r);
+        if (a.out_f32) ((float*)a.out)[at] = res;
+        else ((__nv_bfloat16*)a.out)[at] = __float2bfloat16_rn(res);
       } else {
         const size_t part = ((size_t)t0 * a.H * a.maps + hm) * a.splits + split;
         a.ws_o[part * DV + c] = acc;
@@ -349,7 +382,8 @@ attention_maps_mma_kernel(const MapsArgs a) {
 constexpr int AM_MAX_PARTS = 1024;
 __global__ void __launch_bounds__(128)
 attention_maps_join_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, void* __restrict__ out, long ldo,
-                           int out_f32, const int32_t* __restrict__ tok_seq, int per_tok, int dv, int parts) {
+                           int out_f32, const int32_t* __restrict__ tok_seq, int per_tok, int dv, int parts,
+                           const float* __restrict__ gate, long ldg, int maps) {
   __shared__ float w_s[AM_MAX_PARTS];
   __shared__ float red[32];
   pdl_wait();
@@ -374,7 +408,8 @@ attention_maps_join_kernel(const float* __restrict__ ws_o, const float* __restri
     w_s[s] = w;
     part += w * ml[2 * s + 1];
   }
-  const float inv = 1.0f / block_sum(part, red);
+  float inv = 1.0f / block_sum(part, red);
+  if (gate) inv *= 1.0f / (1.0f + __expf(-gate[(size_t)t * ldg + hm / maps]));
   const float* o = ws_o + (size_t)item * parts * dv;
   for (int c = threadIdx.x; c < dv; c += blockDim.x) {
     float acc = 0.f;
@@ -420,7 +455,8 @@ LLMI_EXPORT int llmi_attention_maps_mma(const void* q, long ldq, void* out, long
                                         const int32_t* seq_kv_len, int n_tokens, int n_seqs, int n_heads, int n_kv_heads, int maps,
                                         int dk, int dv, float scale, const float* head_scale, int window, int chunk, int prompt,
                                         int n_blocks, int splits, int pages_per_split, float* workspace, long workspace_floats,
-                                        cudaStream_t stream) {
+                                        int pool, const void* k_pool, const void* v_pool, const int32_t* pool_pages,
+                                        int pool_pages_stride, const float* gate, long ldg, cudaStream_t stream) {
   if (n_tokens <= 0 || n_seqs <= 0 || n_heads <= 0 || n_kv_heads <= 0 || maps <= 0 || n_heads % n_kv_heads) return LLMI_ERR_BAD_SIZE;
   if (!llmi_attention_maps_mma_supported(dk, dv, n_heads / n_kv_heads, AM_PAGE)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || (ldq % 8) || ((uintptr_t)out & 7) || (ldo % 2))
@@ -433,6 +469,10 @@ LLMI_EXPORT int llmi_attention_maps_mma(const void* q, long ldq, void* out, long
   a.n_seqs = n_seqs; a.H = n_heads; a.G = n_kv_heads; a.maps = maps; a.dk = dk;
   a.scale_log2 = scale * 1.4426950408889634f; a.head_scale = head_scale; a.window = window; a.chunk = chunk;
   a.splits = splits; a.pages_per_split = pages_per_split; a.ws_o = nullptr; a.ws_ml = nullptr;
+  if (pool < 0 || (pool > 0 && (!k_pool || !v_pool || !pool_pages || window <= 0 || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15))))
+    return LLMI_ERR_BAD_SIZE;
+  a.pool = pool; a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
+  a.pool_pages = pool_pages; a.pool_pages_stride = pool_pages_stride; a.gate = gate; a.ldg = ldg;
   const int rows = prompt ? AM_PROMPT_ROWS : 16;
   const int nbuf = prompt ? 2 : AM_TOKEN_BUFFERS;
   const size_t smem = ((size_t)(rows + nbuf * AM_PAGE) * (dk + AM_PAD) + (size_t)nbuf * AM_PAGE * (dv + AM_PAD)) * 2;
@@ -460,5 +500,5 @@ LLMI_EXPORT int llmi_attention_maps_mma(const void* q, long ldq, void* out, long
   const long items = (long)n_tokens * n_heads * maps;
   if (items > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
   return launch_pdl(PDL_SMALL, attention_maps_join_kernel, dim3((unsigned)items), dim3(128), 0, stream, (const float*)a.ws_o,
-                    (const float*)a.ws_ml, out, ldo, out_f32, tok_seq, n_heads * maps, dv, splits);
+                    (const float*)a.ws_ml, out, ldo, out_f32, tok_seq, n_heads * maps, dv, splits, gate, ldg, maps);
 }

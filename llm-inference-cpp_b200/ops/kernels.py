@@ -958,19 +958,25 @@ def attention_maps(q, out, k_cache, v_cache, ctx, seq_pages, page_size: int, n_h
     tensor-core kernel takes go there — prompts as blocks of 128 query rows, steps of single tokens cut over the
     positions (``rt`` lends the workspace of the cuts) —, everything else, and the 32-bit path, to the generic kernel."""
     if (q.dtype == torch.bfloat16 and rt is not None and _MAPS_ATTENTION == "mma" and not _FORCE_GENERIC_ATTENTION
-            and pooled is None and gate is None
             and lib().llmi_attention_maps_mma_supported(c_int(dk), c_int(dv), c_int(n_heads // n_kv_heads), c_int(page_size))
             and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 8 == 0):
-        _need_cuda(q, out, k_cache, v_cache, seq_pages, head_scale)
+        _need_cuda(q, out, k_cache, v_cache, seq_pages, head_scale, gate)
         T = q.shape[0]
         S, P = seq_pages.shape
+        pool, k_pool, v_pool, pool_pages = pooled if pooled is not None else (0, None, None, None)
+        if pool:
+            _need_cuda(k_pool, v_pool, pool_pages)
+            assert window > 0 and k_pool.dtype == v_pool.dtype == torch.bfloat16 and pool_pages.dtype == torch.int32
+            assert k_pool.shape[-3:] == (n_kv_heads * maps, page_size, dk) and v_pool.shape[-3:] == (n_kv_heads, page_size, dv)
+            assert k_pool.is_contiguous() and v_pool.is_contiguous() and pool_pages.shape[0] == S
+        assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == T and gate.shape[1] >= n_heads)
         assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, n_heads * maps * dv) and k_cache.is_contiguous()
         assert v_cache.is_contiguous() and k_cache.shape[-3:] == (n_kv_heads * maps, page_size, dk)
         assert v_cache.shape[-3:] == (n_kv_heads, page_size, dv) and out.dtype in (torch.bfloat16, torch.float32)
         prompt = not ctx.decode
         splits, pps, ws, n_ws = 1, max(P, 1), None, 0
         if not prompt:
-            splits, pps = maps_attention_plan(S, P, n_kv_heads * maps, window, chunk, page_size)
+            splits, pps = maps_attention_plan(S, P, n_kv_heads * maps, window, chunk, page_size, pool)
             n_ws = int(lib().llmi_attention_maps_mma_workspace(c_int(T), c_int(n_heads), c_int(maps), c_int(dv), c_int(splits)))
             ws = rt.scratch("attn_maps_partials", (n_ws,), torch.float32)
         _check("attention_maps_mma", lib().llmi_attention_maps_mma(
@@ -978,7 +984,9 @@ def attention_maps(q, out, k_cache, v_cache, ctx, seq_pages, page_size: int, n_h
             _ptr(k_cache), _ptr(v_cache), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(seq_pages), c_int(seq_pages.stride(0)),
             _ptr(ctx.seq_q_start), _ptr(ctx.seq_kv_len), c_int(T), c_int(S), c_int(n_heads), c_int(n_kv_heads), c_int(maps), c_int(dk),
             c_int(dv), c_float(scale), _ptr(head_scale), c_int(window), c_int(chunk), c_int(1 if prompt else 0),
-            c_int(T // 128 + S), c_int(splits), c_int(pps), _ptr(ws), c_long(n_ws), _stream()))
+            c_int(T // 128 + S), c_int(splits), c_int(pps), _ptr(ws), c_long(n_ws), c_int(pool), _ptr(k_pool), _ptr(v_pool),
+            _ptr(pool_pages), c_int(pool_pages.stride(0) if pool else 0), _ptr(gate),
+            c_long(gate.stride(0) if gate is not None else 0), _stream()))
         return
     attention_flex(q, out, k_cache, v_cache, ctx, seq_pages, page_size, n_heads, n_kv_heads, maps, dk, dv, scale, head_scale,
                    window, chunk, pooled, gate)
@@ -988,7 +996,8 @@ _MAPS_ATTENTION = os.environ.get("LLMI_MAPS_ATTENTION", "mma")      # "generic":
 _MAPS_BLOCKS_PER_SM = int(os.environ.get("LLMI_MAPS_BLOCKS_PER_SM", "3"))
 
 
-def maps_attention_plan(n_seqs: int, n_pages: int, kv_head_maps: int, window: int, chunk: int, page_size: int) -> tuple:
+def maps_attention_plan(n_seqs: int, n_pages: int, kv_head_maps: int, window: int, chunk: int, page_size: int,
+                        pool: int = 0) -> tuple:
     """(cuts over the positions, pages per cut) of the tensor-core attention for a step of single tokens: cut until
     about three blocks per SM are at work (measured, batch 8 at 4,096 positions: 0.639 ms a step with two, 0.626 with three, 0.628 with four, 0.636 with six).  A query sees at most the pages its window or its block of positions spans.
     Depends on the step's padded shape only, so a recorded step can be replayed."""
@@ -996,6 +1005,8 @@ def maps_attention_plan(n_seqs: int, n_pages: int, kv_head_maps: int, window: in
     for span in (window, chunk):
         if span > 0:
             visible = min(visible, -(-span // page_size) + 1)
+    if pool > 0:       # pages of pooled rows ahead of the window's pages: one row per `pool` positions
+        visible += -(-n_pages // pool)
     want = max(1, min(visible, 256, -(-_MAPS_BLOCKS_PER_SM * sm_count() // max(1, n_seqs * kv_head_maps))))
     pps = -(-visible // want)
     return -(-visible // pps), pps

@@ -174,3 +174,13 @@ def forward(cfg, w, tokens, keep_layers=False):
         after.append(x)
     logits = layer_norm(x, w["final.norm"], eps) @ w["head"].T
     return (logits, np.stack(after)) if keep_layers else logits
+
+
+def generate_greedy(cfg, w, prompt, n_new):
+    """The tokens a greedy loop adds to ``prompt`` (the first largest logit each time), recomputing everything."""
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(np.argmax(forward(cfg, w, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
