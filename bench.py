@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload smollm2-360m|smollm2-135m [--workload-dtypes bfloat16,float32]
-    python bench.py --design garodra|fusazen [--design-sizes 2048,1024]          (its own JSON line: that design's prefill and
+    python bench.py --design garodra|fusazen|gemosun [--design-sizes 2048,1024]          (its own JSON line: that design's prefill and
                                                                                   decode beside the Llama decoder at equal size;
                                                                                   garodra also has the size 2048-looped)
 
@@ -289,13 +289,38 @@ FUSAZEN_SIZES = {
 }
 
 
+# --design gemosun: the Gemosun design at sizes that resemble a real model's layers, beside the Llama decoder at equal
+# width, depth and dense feed-forward size.  Eight layers whose feed-forwards alternate: gated dense, then routed experts
+# (eight, two a token, in four groups of which two can be chosen, plus a gated shared expert).  Every mixer is the
+# design's attention: four query heads per key/value head, values that are the keys, a stretched rotation of half a head,
+# a gate per head.  The sizes differ in the mask: a window of 1,024 positions with blocks of 16 pooled behind it (what the
+# design is for: a decode step at 4,096 positions reads 1,024 positions and 192 pooled rows a layer), or ("-full") a
+# window that spans the whole context, so that attention reads as many positions as the Llama decoder's.
+def gemosun_config(width, heads, kv_heads, dim, ff, experts, top, expert_ff, groups, shared, window, pool, layers, vocab):
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+           "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}},
+           "mask": {"size": window, "pool": pool}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "groups": {"count": groups[0], "keep": groups[1]}},
+           "shared": {"ff": shared}}
+    return {"architecture": "Gemosun", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention", "mixer": att, "mlp": (dense, moe)[i % 2]} for i in range(layers)]}
+
+
+GEMOSUN_SIZES = {
+    "2048": (gemosun_config(2048, 16, 4, 128, 8192, 8, 2, 2048, (4, 2), 2048, 1024, 16, 8, 49152), None),
+    "2048-full": (gemosun_config(2048, 16, 4, 128, 8192, 8, 2, 2048, (4, 2), 2048, 8192, 16, 8, 49152), None),
+    "1024": (gemosun_config(1024, 16, 4, 64, 4096, 8, 2, 1024, (4, 2), 1024, 1024, 16, 8, 49152), None),
+}
+
+
 class KernelTimes:
     """Device time per entry point of ops.kernels inside real steps (CUDA events around every call; steps run launch
     by launch while this is on, so the figures are shares of a step, not a benchmark of it)."""
     NAMES = ("embed", "rmsnorm", "swiglu", "linear", "rope_store", "attention", "dyt", "dyt_add", "stream_add", "linear_batched",
              "latent_prepare", "latent_q_rotate", "attention_latent", "delta_step", "delta_finish", "moe_route",
              "moe_experts_streamed", "moe_experts_grouped", "conv_add", "qkv_prepare", "attention_maps", "diff_combine",
-             "gdelta_prepare", "dplr_recurrence", "activate")
+             "gdelta_prepare", "dplr_recurrence", "activate", "layernorm", "depth_mix", "pool_rows", "gate_rows")
 
     def __init__(self):
         self.spans, self.saved = [], {}
@@ -338,10 +363,11 @@ def design_run(name, steps, warmup, batch, context, tokens, sizes):
     import torch
     import llmi_b200 as L
     from llmi_b200 import SequenceStep
-    if name not in ("garodra", "fusazen"):
+    tables = {"garodra": DESIGN_SIZES, "fusazen": FUSAZEN_SIZES, "gemosun": GEMOSUN_SIZES}
+    if name not in tables:
         print(f"bench.py: unknown design {name!r}")
         return 2
-    table = DESIGN_SIZES if name == "garodra" else FUSAZEN_SIZES
+    table = tables[name]
     pk, pk_kind = peaks()
     out = {"design": name, "impl": "ours", "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids, random cache contents)",
            "batch": batch, "context": context, "prefill_tokens": tokens, "steps": steps, "warmup": warmup, "peaks": pk_kind,
@@ -349,7 +375,7 @@ def design_run(name, steps, warmup, batch, context, tokens, sizes):
     for size in sizes:
         g_cfg, l_cfg = table[size]
         if l_cfg is None:
-            l_cfg = DESIGN_SIZES[size][1]
+            l_cfg = DESIGN_SIZES[size.split("-")[0]][1]
         row = {}
         for label, cfg in ((name, g_cfg), ("llama", l_cfg)):
             model = L.random_model(cfg, seed=0, dtype="bfloat16", on_device=True)
@@ -408,9 +434,9 @@ def main():
     ap.add_argument("--kv-heads", type=int, default=None,
                     help="with --only: another number of key/value heads (grouped queries), to profile their kernels")
     ap.add_argument("--design", default=None,
-                    help="'garodra' or 'fusazen': that design's prefill and decode throughput at layer sizes of a real model, beside the "
+                    help="'garodra', 'fusazen' or 'gemosun': that design's prefill and decode throughput at layer sizes of a real model, beside the "
                          "Llama decoder at equal size (its own JSON line; the default workload is untouched)")
-    ap.add_argument("--design-sizes", default="2048,1024", help="with --design: which of " + ", ".join(sorted(DESIGN_SIZES)))
+    ap.add_argument("--design-sizes", default="2048,1024", help="with --design: which of " + ", ".join(sorted(set(DESIGN_SIZES) | set(GEMOSUN_SIZES))))
     args = ap.parse_args()
 
     if args.design:
