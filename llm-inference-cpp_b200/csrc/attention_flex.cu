@@ -199,6 +199,50 @@ pool_rows_kernel(const T* __restrict__ k_cache, const T* __restrict__ v_cache, P
   }
 }
 
+// The same for bf16 rows of whole 16-byte pieces: a thread owns one piece (8 entries) of a head's row and adds the
+// block's rows in position order; blockIdx.y cuts the pieces of a row over several blocks.
+__global__ void __launch_bounds__(128)
+pool_rows_vec_kernel(const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache, PagedKV kp, PagedKV vp,
+                     __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, PagedKV kpp, PagedKV vpp, int pool,
+                     const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int seq = tok_seq[t];
+  if (seq < 0) return;
+  const int pos = tok_pos[t];
+  if ((pos + 1) % pool != 0) return;
+  const int b = pos / pool, first = pos - pool + 1;
+  const float inv = 1.0f / (float)pool;
+  const int nk = kp.n_kv_heads * kp.head_dim / 8, nv = vp.n_kv_heads * vp.head_dim / 8;
+  for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < nk + nv; idx += gridDim.y * blockDim.x) {
+    const bool is_k = idx < nk;
+    const PagedKV& src = is_k ? kp : vp;
+    const int i = is_k ? idx : idx - nk;
+    const int per = src.head_dim / 8;
+    const int hd = i / per, e = (i - hd * per) * 8;
+    const __nv_bfloat16* cache = is_k ? k_cache : v_cache;
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int j = 0; j < pool; ++j) {
+      const uint4 u = *reinterpret_cast<const uint4*>(cache + kv_row_offset(src, seq, first + j, hd) + e);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const float2 f = __bfloat1622float2(h[x]);
+        sum[2 * x] += f.x;
+        sum[2 * x + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int x = 0; x < 4; ++x) oh[x] = __floats2bfloat162_rn(sum[2 * x] * inv, sum[2 * x + 1] * inv);
+    __nv_bfloat16* dst = is_k ? k_pool + kv_row_offset(kpp, seq, b, hd) + e : v_pool + kv_row_offset(vpp, seq, b, hd) + e;
+    *reinterpret_cast<uint4*>(dst) = o;
+  }
+}
+
 template <typename T, typename OutT>
 int launch_attention_flex(const void* q, long ldq, void* out, long ldo, const void* k_cache, const void* v_cache,
                           const int32_t* tok_seq, const int32_t* tok_pos, PagedKV kp, PagedKV vp, int n_tokens, int n_heads,
@@ -286,6 +330,14 @@ LLMI_EXPORT int llmi_pool_rows(int dtype, const void* k_cache, const void* v_cac
   if (dtype == LLMI_DTYPE_F32)
     return launch_pdl(PDL_SMALL, pool_rows_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, (const float*)k_cache,
                       (const float*)v_cache, kp, vp, (float*)k_pool, (float*)v_pool, kpp, vpp, pool, tok_seq, tok_pos);
+  if (dtype == LLMI_DTYPE_BF16 && dk % 8 == 0 && dv % 8 == 0 && !((uintptr_t)k_cache & 15) && !((uintptr_t)v_cache & 15) &&
+      !((uintptr_t)k_pool & 15) && !((uintptr_t)v_pool & 15)) {
+    const int pieces = (n_k_heads * dk + n_v_heads * dv) / 8;
+    const int cuts = n_tokens <= 64 ? (pieces + 127) / 128 : 1;       // few tokens: a row's pieces over several blocks
+    return launch_pdl(PDL_SMALL, pool_rows_vec_kernel, dim3(n_tokens, cuts), dim3(128), 0, stream, (const __nv_bfloat16*)k_cache,
+                      (const __nv_bfloat16*)v_cache, kp, vp, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, kpp, vpp, pool, tok_seq,
+                      tok_pos);
+  }
   if (dtype == LLMI_DTYPE_BF16)
     return launch_pdl(PDL_SMALL, pool_rows_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), 0, stream, (const __nv_bfloat16*)k_cache,
                       (const __nv_bfloat16*)v_cache, kp, vp, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, kpp, vpp, pool, tok_seq,

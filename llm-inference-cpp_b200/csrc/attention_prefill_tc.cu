@@ -77,6 +77,14 @@ struct PrefillTcParams {
   int split_pages;          // 0: a query block's keys are one job; else jobs of at most this many pages
   float* partials;          // [job (gridDim.y)][head][HD + 2][128]: per row m_ref, l, O[HD], when split
   int* tickets;             // [n_tiles * n_heads], zero before and after the launch
+  // Pooled blocks ahead of the window (pool > 0, window > 0): block b of `pool` positions has ONE key and value row, row b
+  // of the sequence's pooled pages (a cache and page table of their own); the query at position p sees the blocks with
+  // b * pool + pool - 1 <= p - window.  A query block walks the pooled pages it can see first, then its token pages.
+  int pool;
+  const int32_t* pool_pages;
+  int pool_pages_stride;
+  const float* gate;        // [tokens, >= n_heads] fp32 or null: head h's output times logistic(gate[t, h])
+  long ldg;
 };
 
 __device__ __forceinline__ void ft_tma(uint32_t dst, const CUtensorMap* map, int col, int row, uint32_t bar) {
@@ -144,7 +152,8 @@ __device__ __forceinline__ void ft_st16u(uint32_t taddr, const uint32_t* v) {
 template <int HD>
 __global__ void __launch_bounds__(FtCfg<HD>::THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                            const __grid_constant__ CUtensorMap map_v, PrefillTcParams p) {
+                            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_kp,
+                            const __grid_constant__ CUtensorMap map_vp, PrefillTcParams p) {
   using C = FtCfg<HD>;
   constexpr int STAGES = C::STAGES, NSUB = C::NSUB, HALVES = C::HALVES, KEYS = C::KEYS;
   extern __shared__ uint8_t smem_raw[];
@@ -170,6 +179,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int job = blockIdx.y;
   int seq = p.n_seqs - 1, mb = 0, part = 0, n_parts = 1, tile_id = p.n_tiles;
   int q_start = 0, q_len = 0, kv_len = 0, pos0 = 0, m0 = 0, rows_here = 0, first_q = 0, last_q = 0, pg_first = 0, n_pg = 0;
+  int nb_max = 0, n_ppg = 0, v_first = 0;      // pooled blocks and pages the query block sees; this part's first page of all
   {
     int x = job;
     bool found = false;
@@ -186,7 +196,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         last_q = first_q + rows_here - 1;
         const int lo_key = (p.window > 0 && first_q - p.window + 1 > 0) ? first_q - p.window + 1 : 0;
         pg_first = lo_key / FT_PAGE;
-        n_pg = last_q / FT_PAGE - pg_first + 1;
+        nb_max = (p.pool > 0 && last_q - p.window + 1 > 0) ? (last_q - p.window + 1) / p.pool : 0;
+        n_ppg = (nb_max + FT_PAGE - 1) / FT_PAGE;
+        n_pg = n_ppg + last_q / FT_PAGE - pg_first + 1;           // pooled pages, then token pages
         n_parts = p.split_pages > 0 ? (n_pg + p.split_pages - 1) / p.split_pages : 1;
         if (x < n_parts) {
           part = x;
@@ -200,9 +212,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (!found) return;
   }
   if (n_parts > 1) {                       // this block's part of the key range
-    pg_first += part * p.split_pages;
+    v_first = part * p.split_pages;
     n_pg = min(p.split_pages, n_pg - part * p.split_pages);
   }
+  // page j of this part: pooled page v_first + j while that is below n_ppg, else token page pg_first + (v_first + j - n_ppg)
+  const int32_t* ppages = p.pool > 0 ? p.pool_pages + (size_t)seq * p.pool_pages_stride : nullptr;
   const int head = blockIdx.x;
   const int kvh = head / (p.n_heads / p.n_kv_heads);
   const int32_t* pages = p.seq_pages + (size_t)seq * p.pages_stride;
@@ -214,6 +228,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+    if (p.pool > 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_kp) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_vp) : "memory");
+    }
     mbar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(kv_full(s), 1);
@@ -247,12 +265,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int j = 0; j < n_pg; ++j) {
         const int s = j % STAGES;
         if (j >= STAGES && !mbar_wait(kv_empty(s), ((j / STAGES) - 1) & 1, p.error_flag, 41)) break;
-        const int row = (pages[pg_first + j] * p.n_kv_heads + kvh) * FT_PAGE;
+        const int v = v_first + j;
+        const bool pooled = v < n_ppg;
+        const int row = ((pooled ? ppages[v] : pages[pg_first + v - n_ppg]) * p.n_kv_heads + kvh) * FT_PAGE;
+        const CUtensorMap* mk = pooled ? &map_kp : &map_k;
+        const CUtensorMap* mv = pooled ? &map_vp : &map_v;
         mbar_expect_tx(kv_full(s), 2 * C::TILE);
 #pragma unroll
         for (int u = 0; u < NSUB; ++u) {
-          ft_tma(kv_smem + s * 2 * C::TILE + u * FT_SUB, &map_k, 64 * u, row, kv_full(s));
-          ft_tma(kv_smem + s * 2 * C::TILE + C::TILE + u * FT_SUB, &map_v, 64 * u, row, kv_full(s));
+          ft_tma(kv_smem + s * 2 * C::TILE + u * FT_SUB, mk, 64 * u, row, kv_full(s));
+          ft_tma(kv_smem + s * 2 * C::TILE + C::TILE + u * FT_SUB, mv, 64 * u, row, kv_full(s));
         }
       }
     }
@@ -330,10 +352,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
       for (int c = 0; c < KEYS; c += 16) ft_ld16(t_s + (uint32_t)c, sc + c);
       ft_ld_wait();
-      const int page_key0 = (pg_first + j) * FT_PAGE;
+      const int v = v_first + j;
+      const bool pooled = v < n_ppg;
+      // a pooled page: `page_key0` counts blocks; its rows from the first one that no query of this block sees are unused
+      const int page_key0 = (pooled ? v : pg_first + v - n_ppg) * FT_PAGE;
       const int key0 = page_key0 + KEYS * half;
-      const bool need_mask = (key0 + KEYS - 1 > first_q) || (p.window > 0);
-      if (need_mask) {
+      if (pooled) {
+        const int seen = qpos - p.window + 1 > 0 ? (qpos - p.window + 1) / p.pool : 0;      // blocks this query sees
+#pragma unroll
+        for (int c = 0; c < KEYS; ++c)
+          if (key0 + c >= seen) sc[c] = -INFINITY;
+      } else if ((key0 + KEYS - 1 > first_q) || (p.window > 0)) {
 #pragma unroll
         for (int c = 0; c < KEYS; ++c) {
           const int key = key0 + c;
@@ -398,11 +427,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
       for (int c = 0; c < KEYS / 2; c += 16) ft_st16u(t_s + (uint32_t)c, packed + c);
       ft_st_wait();
-      if (page_key0 + FT_PAGE > kv_len) {
+      const int rows_end = pooled ? nb_max : kv_len;
+      if (page_key0 + FT_PAGE > rows_end) {
         // The sequence ends inside this page: value rows behind its end are cleared so that their zero
         // probabilities cannot meet a NaN.  (The page is in shared memory: S_j was computed from it.)
         const uint32_t v_tile = kv_smem + (j % STAGES) * 2 * C::TILE + C::TILE;
-        const int first_bad = kv_len - page_key0;
+        const int first_bad = rows_end - page_key0;
         for (int idx = (warp - 2) * 32 + lane; idx < (FT_PAGE - first_bad) * 8 * NSUB; idx += 128 * HALVES) {
           const int r = first_bad + (idx >> 3) / NSUB, u = (idx >> 3) % NSUB, ch = idx & 7;
           asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(v_tile + (uint32_t)(u * FT_SUB + r * 128 + (ch << 4))), "r"(0u) : "memory");
@@ -478,7 +508,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
       }
       if (write_out) {      // every lane takes part in the TMEM loads; only the rows that exist are stored
-        const float inv = 1.f / L;
+        float inv = 1.f / L;
+        if (p.gate && row_ok) inv *= 1.0f / (1.0f + expf(-p.gate[(size_t)(q_start + qrow) * p.ldg + head]));
         __nv_bfloat16* dst = p.out + (size_t)(q_start + qrow) * p.ldo + (size_t)head * HD + DH * half;
 #pragma unroll 1
         for (int c0 = 0; c0 < DH; c0 += 32) {
@@ -562,8 +593,8 @@ LLMI_EXPORT int llmi_attention_prefill_tc_supported(int head_dim) { return head_
 
 namespace llmi {
 template <int HD>
-static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillTcParams& p, dim3 grid,
-                     cudaStream_t stream) {
+static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mkp,
+                     const CUtensorMap& mvp, const PrefillTcParams& p, dim3 grid, cudaStream_t stream) {
   using C = FtCfg<HD>;
   static PerDevice<bool> configured_on;
   bool& configured = configured_on.here();
@@ -574,18 +605,24 @@ static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
   }
   // a programmatic dependent: its blocks set themselves up (barriers, tensor memory, descriptors) while the kernel
   // before drains; the producer waits before its first copy, and nothing else reads or writes global memory earlier
-  return launch_pdl(PDL_ATTENTION, attention_prefill_tc_kernel<HD>, grid, dim3(C::THREADS), C::SMEM, stream, mq, mk, mv, p);
+  return launch_pdl(PDL_ATTENTION, attention_prefill_tc_kernel<HD>, grid, dim3(C::THREADS), C::SMEM, stream, mq, mk, mv, mkp, mvp, p);
 }
 }  // namespace llmi
 
 // q: [n_tokens, >= n_heads*head_dim] rotated queries (row pitch ldq, 16-byte aligned rows); otherwise as llmi_attention_prefill.
+// pool > 0 (with a window): one pooled key and value row per block of `pool` positions that lies wholly before a
+// query's window, in k_pool / v_pool [n_pool_cache_pages, n_kv_heads, 64, head_dim] under the page table pool_pages
+// [n_seqs, pool_pages_stride] (row b of a sequence's pooled pages is block b); they share the softmax with the window's
+// keys.  gate (optional): fp32 [n_tokens, ldg], head h's output is multiplied by logistic(gate[t, h]).
 // With split_pages > 0: partials holds n_jobs * n_heads * (head_dim + 2) * 128 floats.
 LLMI_EXPORT int llmi_attention_prefill_tc(const void* q, long ldq, long n_tokens, void* out, long ldo, const void* k_cache,
                                           const void* v_cache, long n_cache_pages, const int32_t* seq_pages,
                                           int pages_stride, const int32_t* seq_q_start, const int32_t* seq_kv_len,
                                           int n_seqs, int n_blocks, int n_heads, int n_kv_heads, int head_dim, float scale,
                                           int window, int n_jobs, int split_pages, float* partials, long partials_floats,
-                                          int* tickets, int n_tickets, int* error_flag, cudaStream_t stream) {
+                                          int* tickets, int n_tickets, int* error_flag, int pool, const void* k_pool,
+                                          const void* v_pool, long n_pool_cache_pages, const int32_t* pool_pages,
+                                          int pool_pages_stride, const float* gate, long ldg, cudaStream_t stream) {
   if (n_seqs <= 0 || n_blocks <= 0 || n_heads <= 0 || n_kv_heads <= 0 || n_cache_pages <= 0 || n_tokens <= 0) return LLMI_ERR_BAD_SIZE;
   if (n_heads % n_kv_heads) return LLMI_ERR_BAD_SIZE;
   if (!llmi_attention_prefill_tc_supported(head_dim)) return LLMI_ERR_UNSUPPORTED;
@@ -601,6 +638,20 @@ LLMI_EXPORT int llmi_attention_prefill_tc(const void* q, long ldq, long n_tokens
   if (rc != LLMI_OK) return rc;
   rc = ft_make_map(&mv, v_cache, rows, head_dim, head_dim, FT_PAGE);
   if (rc != LLMI_OK) return rc;
+  CUtensorMap mkp = mk, mvp = mv;
+  if (pool > 0) {
+    // pooled rows ahead of the window: pages of the same shape in a cache of their own
+    if (window <= 0 || !k_pool || !v_pool || !pool_pages || n_pool_cache_pages <= 0 || scale <= 0.f) return LLMI_ERR_BAD_SIZE;
+    if (((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15)) return LLMI_ERR_ALIGN;
+    const long prows = n_pool_cache_pages * n_kv_heads * FT_PAGE;
+    if (prows > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
+    rc = ft_make_map(&mkp, k_pool, prows, head_dim, head_dim, FT_PAGE);
+    if (rc != LLMI_OK) return rc;
+    rc = ft_make_map(&mvp, v_pool, prows, head_dim, head_dim, FT_PAGE);
+    if (rc != LLMI_OK) return rc;
+  } else {
+    pool = 0;
+  }
   // n_jobs: blocks along y — n_blocks without a split, else the sum over the query blocks of their parts (the caller
   // counts them with the same rule as the kernel); the workspace holds one slot per job and head
   if (split_pages > 0) {
@@ -611,8 +662,9 @@ LLMI_EXPORT int llmi_attention_prefill_tc(const void* q, long ldq, long n_tokens
     n_jobs = n_blocks;
   }
   PrefillTcParams p{(__nv_bfloat16*)out, ldo, seq_pages, seq_q_start, seq_kv_len, pages_stride, n_seqs, n_heads,
-                    n_kv_heads, scale * 1.4426950408889634f, window, error_flag, n_blocks, split_pages, partials, tickets};
+                    n_kv_heads, scale * 1.4426950408889634f, window, error_flag, n_blocks, split_pages, partials, tickets,
+                    pool, pool_pages, pool_pages_stride, gate, ldg};
   if (n_jobs > 65535) return LLMI_ERR_BAD_SIZE;
   dim3 grid(n_heads, n_jobs);
-  return head_dim == 64 ? ft_launch<64>(mq, mk, mv, p, grid, stream) : ft_launch<128>(mq, mk, mv, p, grid, stream);
+  return head_dim == 64 ? ft_launch<64>(mq, mk, mv, mkp, mvp, p, grid, stream) : ft_launch<128>(mq, mk, mv, mkp, mvp, p, grid, stream);
 }

@@ -179,7 +179,7 @@ moe_up_kernel(const T* __restrict__ h, long ldh, const T* __restrict__ wg, const
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 moe_down_kernel(const float* __restrict__ a, const T* __restrict__ wd, int W, int F, int top, const int32_t* __restrict__ idx,
-                const float* __restrict__ wt, float* __restrict__ y, long ldy) {
+                const float* __restrict__ wt, float* __restrict__ y, long ldy, int add) {
   extern __shared__ float a_s[];
   pdl_launch_dependents();
   pdl_wait();
@@ -196,7 +196,7 @@ moe_down_kernel(const float* __restrict__ a, const T* __restrict__ wd, int W, in
     const float s = warp_dot<T, VEC>(a_s + (size_t)j * F, wd + ((size_t)e * W + c) * F, F, lane);
     total = fmaf(wt[(size_t)t * top + j], s, total);
   }
-  if (lane == 0) y[(size_t)t * ldy + c] = total;
+  if (lane == 0) y[(size_t)t * ldy + c] = add ? y[(size_t)t * ldy + c] + total : total;
 }
 
 }  // namespace llmi
@@ -234,7 +234,7 @@ static int launch_moe_up(const void* h, long ldh, const void* wg, const void* wu
 
 template <typename T, bool VEC>
 static int launch_moe_down(const float* a, const void* wd, int W, int F, int top, const int32_t* idx, const float* wt, float* y, long ldy,
-                           int n_tokens, cudaStream_t stream) {
+                           int n_tokens, int add, cudaStream_t stream) {
   const size_t smem = (size_t)top * F * 4;
   static PerDevice<size_t> allowed;
   if (smem > 48 * 1024 && allowed.here() < smem) {
@@ -243,7 +243,7 @@ static int launch_moe_down(const float* a, const void* wd, int W, int F, int top
     allowed.here() = smem;
   }
   return launch_pdl(PDL_GEMM, moe_down_kernel<T, VEC>, dim3(n_tokens, (W + 7) / 8), dim3(256), smem, stream, a, (const T*)wd, W, F, top,
-                    idx, wt, y, ldy);
+                    idx, wt, y, ldy, add);
 }
 
 LLMI_EXPORT int llmi_moe_up(int dtype, const void* h, long ldh, const void* wg, const void* wu, int W, int F, int top,
@@ -264,15 +264,15 @@ LLMI_EXPORT int llmi_moe_up(int dtype, const void* h, long ldh, const void* wg, 
 }
 
 LLMI_EXPORT int llmi_moe_down(int dtype, const float* a, const void* wd, int W, int F, int top, const int32_t* idx,
-                              const float* wt, float* y, long ldy, int n_tokens, cudaStream_t stream) {
+                              const float* wt, float* y, long ldy, int n_tokens, int add, cudaStream_t stream) {
   if (n_tokens <= 0 || W <= 0 || F <= 0 || top <= 0 || (size_t)top * F * 4 > 160 * 1024 || (W + 7) / 8 > 65535) return LLMI_ERR_BAD_SIZE;
   const int esz = dtype == LLMI_DTYPE_F32 ? 4 : 2;
   const bool vec = ((size_t)F * esz) % 16 == 0 && !((uintptr_t)wd & 15);
   if (dtype == LLMI_DTYPE_F32)
-    return vec ? launch_moe_down<float, true>(a, wd, W, F, top, idx, wt, y, ldy, n_tokens, stream)
-               : launch_moe_down<float, false>(a, wd, W, F, top, idx, wt, y, ldy, n_tokens, stream);
+    return vec ? launch_moe_down<float, true>(a, wd, W, F, top, idx, wt, y, ldy, n_tokens, add, stream)
+               : launch_moe_down<float, false>(a, wd, W, F, top, idx, wt, y, ldy, n_tokens, add, stream);
   if (dtype == LLMI_DTYPE_BF16)
-    return vec ? launch_moe_down<__nv_bfloat16, true>(a, wd, W, F, top, idx, wt, y, ldy, n_tokens, stream)
-               : launch_moe_down<__nv_bfloat16, false>(a, wd, W, F, top, idx, wt, y, ldy, n_tokens, stream);
+    return vec ? launch_moe_down<__nv_bfloat16, true>(a, wd, W, F, top, idx, wt, y, ldy, n_tokens, add, stream)
+               : launch_moe_down<__nv_bfloat16, false>(a, wd, W, F, top, idx, wt, y, ldy, n_tokens, add, stream);
   return LLMI_ERR_BAD_DTYPE;
 }

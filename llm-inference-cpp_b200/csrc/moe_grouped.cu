@@ -214,7 +214,7 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ A, long lda, const int32_t*
 // One block per token: y[t] = sum_j wt[t, j] * ys[item_pos[t * top + j]] in the order of j.
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ ys, const int32_t* __restrict__ item_pos, const float* __restrict__ wt, int top,
-                   int W, float* __restrict__ y, long ldy) {
+                   int W, float* __restrict__ y, long ldy, int add) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -224,7 +224,7 @@ moe_combine_kernel(const float* __restrict__ ys, const int32_t* __restrict__ ite
       const int pos = item_pos[(size_t)t * top + j];
       if (pos >= 0) total = fmaf(wt[(size_t)t * top + j], ys[(size_t)pos * W + c], total);
     }
-    y[(size_t)t * ldy + c] = total;
+    y[(size_t)t * ldy + c] = add ? y[(size_t)t * ldy + c] + total : total;
   }
 }
 
@@ -241,7 +241,7 @@ LLMI_EXPORT long llmi_moe_group_ints(int n_items, int E) {
 
 LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const void* wu, const void* wd, int W, int F, int E,
                                  int top, const int32_t* idx, const float* wt, int act, int32_t* scratch, long scratch_ints,
-                                 void* a_sorted, float* y_sorted, float* y, long ldy, int n_tokens, cudaStream_t stream) {
+                                 void* a_sorted, float* y_sorted, float* y, long ldy, int n_tokens, int add, cudaStream_t stream) {
   if (n_tokens <= 0 || W <= 0 || F <= 0 || E <= 0 || E > 256 || top <= 0) return LLMI_ERR_BAD_SIZE;
   if ((W % 8) || (F % 8) || (ldh % 8) || ((uintptr_t)h & 15) || ((uintptr_t)wg & 15) || ((uintptr_t)wu & 15) || ((uintptr_t)wd & 15) ||
       ((uintptr_t)a_sorted & 15))
@@ -295,7 +295,7 @@ LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const 
                   (const int32_t*)tile_row0, (const int32_t*)n_tiles, (void*)y_sorted, (long)W, 0, 0L, 0L);
   if (rc != LLMI_OK) return rc;
   return launch_pdl(PDL_SMALL, moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)y_sorted,
-                    (const int32_t*)item_pos, wt, top, W, y, ldy);
+                    (const int32_t*)item_pos, wt, top, W, y, ldy, add);
 }
 
 // `batch` products of equal sizes on the tensor cores (bf16), one per head: out[:, b*by : b*by+N] = x[:, b*bx : b*bx+K] . w[b]^T,

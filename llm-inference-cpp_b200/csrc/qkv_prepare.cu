@@ -10,7 +10,7 @@
 //   * q goes to `q_out` in the compute type; k and v go to the cache pages of (sequence, position).
 // Keys and values may differ in their number of heads and in their head size (two page layouts).  With `v_from_k`
 // the row has no v part: the values are the key rows as projected (after the norm, before the rotation), head for head.
-// All arithmetic is fp32; one block per token.
+// All arithmetic is fp32; one block per token, or, where no norm ties a part's heads together, one per (token, head).
 #include "common.cuh"
 #include "step_meta.cuh"
 
@@ -100,6 +100,77 @@ qkv_prepare_kernel(const float* __restrict__ proj, long ld, int n_q_heads, int n
   }
 }
 
+// Without the norms over the whole q and k parts a head needs nothing of its neighbours: one block per (token, head) —
+// the q heads, then the k heads, then (unless the values are the keys) the v heads — with the same arithmetic per entry.
+template <typename T>
+__device__ __forceinline__ void prepare_head(const float* __restrict__ proj, long ld, int n_q_heads, int n_k_heads, int dk, int dv,
+                                             const float* __restrict__ inv_freq, int rot_dims, int pairing, float amplitude,
+                                             int v_from_k, int seq, const int32_t* __restrict__ tok_pos, const PagedKV& kp,
+                                             const PagedKV& vp, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                             T* __restrict__ q_out, long ldq, int t, int hd) {
+  if (hd < n_q_heads) {
+    T* qo = q_out + (size_t)t * ldq + (size_t)hd * dk;
+    if (seq < 0) {
+      for (int i = threadIdx.x; i < dk; i += blockDim.x) qo[i] = from_f32<T>(0.f);
+      return;
+    }
+    prepare_part<T>(proj + (size_t)t * ld + (size_t)hd * dk, 1, dk, 1.f, nullptr, inv_freq, rot_dims, pairing, amplitude, tok_pos[t],
+                    [&](int) { return qo; }, NoCopy());
+    return;
+  }
+  if (seq < 0) return;
+  const int pos = tok_pos[t];
+  const float* krow = proj + (size_t)t * ld + (size_t)n_q_heads * dk;
+  if (hd < n_q_heads + n_k_heads) {
+    const int kh = hd - n_q_heads;
+    T* ko = k_cache + kv_row_offset(kp, seq, pos, kh);
+    if (v_from_k) {
+      T* vo = v_cache + kv_row_offset(vp, seq, pos, kh);
+      prepare_part<T>(krow + (size_t)kh * dk, 1, dk, 1.f, nullptr, inv_freq, rot_dims, pairing, amplitude, pos,
+                      [&](int) { return ko; }, [&](int) { return (void*)vo; });
+    } else {
+      prepare_part<T>(krow + (size_t)kh * dk, 1, dk, 1.f, nullptr, inv_freq, rot_dims, pairing, amplitude, pos,
+                      [&](int) { return ko; }, NoCopy());
+    }
+    return;
+  }
+  const int vh = hd - n_q_heads - n_k_heads;
+  const float* vrow = krow + (size_t)n_k_heads * dk + (size_t)vh * dv;
+  T* vo = v_cache + kv_row_offset(vp, seq, pos, vh);
+  for (int e = threadIdx.x; e < dv; e += blockDim.x) vo[e] = from_f32<T>(vrow[e]);
+}
+
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+qkv_prepare_heads_kernel(const float* __restrict__ proj, long ld, int n_q_heads, int n_k_heads, int dk, int n_v_heads, int dv,
+                         const float* __restrict__ inv_freq, int rot_dims, int pairing, float amplitude, int v_from_k,
+                         const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos, PagedKV kp, PagedKV vp,
+                         T* __restrict__ k_cache, T* __restrict__ v_cache, T* __restrict__ q_out, long ldq, int write_kv,
+                         int heads_per_block) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int seq = tok_seq[t];
+  const int n_all = n_q_heads + (write_kv ? n_k_heads + (v_from_k ? 0 : n_v_heads) : 0);
+  for (int hd = blockIdx.y * heads_per_block; hd < min(n_all, (int)(blockIdx.y + 1) * heads_per_block); ++hd)
+    prepare_head<T>(proj, ld, n_q_heads, n_k_heads, dk, dv, inv_freq, rot_dims, pairing, amplitude, v_from_k, seq, tok_pos, kp, vp,
+                    k_cache, v_cache, q_out, ldq, t, hd);
+}
+
+template <typename T>
+static int launch_prepare_heads(const float* proj, long ld, int n_q_heads, int n_k_heads, int dk, int n_v_heads, int dv,
+                                const float* inv_freq, int rot_dims, int pairing, float amplitude, int v_from_k,
+                                const int32_t* tok_seq, const int32_t* tok_pos, PagedKV kp, PagedKV vp, void* k_cache, void* v_cache,
+                                void* q_out, long ldq, int n_tokens, bool kv, cudaStream_t stream) {
+  const int heads = n_q_heads + (kv ? n_k_heads + (v_from_k ? 0 : n_v_heads) : 0);
+  // few tokens: a head per block of 64 threads; many: four heads per block of 128 (fewer, longer blocks)
+  const int per = n_tokens <= 128 ? 1 : 4, threads = n_tokens <= 128 ? 64 : 128;
+  return launch_pdl(PDL_SMALL, qkv_prepare_heads_kernel<T>, dim3(n_tokens, (heads + per - 1) / per), dim3(threads), 0, stream, proj, ld,
+                    n_q_heads, n_k_heads, dk, n_v_heads, dv, inv_freq, rot_dims, pairing, amplitude, v_from_k, tok_seq, tok_pos, kp, vp,
+                    (T*)k_cache, (T*)v_cache, (T*)q_out, ldq, kv ? 1 : 0, per);
+}
+
 }  // namespace llmi
 
 using namespace llmi;
@@ -116,6 +187,17 @@ LLMI_EXPORT int llmi_qkv_prepare(int dtype, const float* proj, long ld, int n_q_
   if (rot_dims < 0 || rot_dims > dk || (rot_dims & 1) || (rot_dims > 0 && !inv_freq)) return LLMI_ERR_BAD_SIZE;
   if (v_from_k && (!has_kv || n_v_heads != n_k_heads || dv != dk)) return LLMI_ERR_BAD_SIZE;
   const PagedKV kp{k_pages, k_pages_stride, page_size, n_k_heads, dk}, vp{v_pages, v_pages_stride, page_size, n_v_heads, dv};
+  if (!q_norm_w && !k_norm_w && n_q_heads + n_k_heads + n_v_heads <= 65535) {
+    const bool kv = has_kv && write_kv;
+    if (dtype == LLMI_DTYPE_F32)
+      return launch_prepare_heads<float>(proj, ld, n_q_heads, n_k_heads, dk, n_v_heads, dv, inv_freq, rot_dims, pairing, amplitude,
+                                         v_from_k, tok_seq, tok_pos, kp, vp, k_cache, v_cache, q_out, ldq, n_tokens, kv, stream);
+    if (dtype == LLMI_DTYPE_BF16)
+      return launch_prepare_heads<__nv_bfloat16>(proj, ld, n_q_heads, n_k_heads, dk, n_v_heads, dv, inv_freq, rot_dims, pairing,
+                                                 amplitude, v_from_k, tok_seq, tok_pos, kp, vp, k_cache, v_cache, q_out, ldq, n_tokens,
+                                                 kv, stream);
+    return LLMI_ERR_BAD_DTYPE;
+  }
   if (dtype == LLMI_DTYPE_F32)
     return launch_pdl(PDL_SMALL, qkv_prepare_kernel<float>, dim3(n_tokens), dim3(128), 0, stream, proj, ld, n_q_heads, n_k_heads,
                       dk, n_v_heads, dv, q_norm_w, k_norm_w, eps, inv_freq, rot_dims, pairing, amplitude, v_from_k, tok_seq, tok_pos, kp, vp, (float*)k_cache,

@@ -197,12 +197,17 @@ class Model:
                 nxt = (getattr(blocks[i + 1], "entry_norm", None)
                        if i + 1 < len(blocks) and self.entries[i + 1] is None and self.exits[i] is None else None)
                 entry = block.forward(x, ctx, binding, entry=entry, next_norm=nxt)
+            elif hasattr(block, "entry_norms"):
+                block.forward(x, ctx, binding, entry=entry)
+                entry = None
             else:
                 block.forward(x, ctx, binding)
                 entry = None
             if self.exits[i] is not None:
-                self.exits[i].forward(x, history, i, ctx)
-                entry = None                 # (the stream has changed since the block looked at it)
+                # what acts behind the call may make the next block's first norms in the same pass over the stream
+                then = (getattr(blocks[i + 1], "entry_norms", None)
+                        if i + 1 < len(blocks) and self.entries[i + 1] is None else None)
+                entry = self.exits[i].forward(x, history, i, ctx, then=then) if then is not None else self.exits[i].forward(x, history, i, ctx)
             elif history is not None:
                 history[i + 1].copy_(x)
             if trace is not None:

@@ -160,7 +160,7 @@ def lib():
                      "llmi_moe_down", "llmi_moe_grouped", "llmi_linear_heads_mma", "llmi_attention_latent_mma", "llmi_attention_latent_mma_supported",
                      "llmi_conv_add", "llmi_conv_carry", "llmi_qkv_prepare", "llmi_attention_flex", "llmi_diff_combine",
                      "llmi_gdelta_prepare", "llmi_dplr_recurrence", "llmi_activate", "llmi_attention_maps_mma", "llmi_attention_maps_mma_supported", "llmi_tanh_rows", "llmi_norm_conv_token",
-                     "llmi_layernorm", "llmi_depth_mix", "llmi_gate_rows", "llmi_pool_rows"):
+                     "llmi_layernorm", "llmi_depth_mix", "llmi_gate_rows", "llmi_pool_rows", "llmi_mix_layernorm"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_delta_state_floats.restype = c_long
@@ -174,7 +174,7 @@ def lib():
         l.llmi_gemm_tc.argtypes = [P, L, P, L, P, P, L, I, I, I, I, P, L, P, I, P, P]
         l.llmi_rmsnorm.argtypes = [I, P, P, P, P, I, I, F, P]
         l.llmi_rope_store.argtypes = [I, P, L, P, I, P, P, P, I, I, P, P, I, I, I, I, I, P]
-        l.llmi_attention_prefill_tc.argtypes = [P, L, L, P, L, P, P, L, P, I, P, P, I, I, I, I, I, F, I, I, I, P, L, P, I, P, P]
+        l.llmi_attention_prefill_tc.argtypes = [P, L, L, P, L, P, P, L, P, I, P, P, I, I, I, I, I, F, I, I, I, P, L, P, I, P, I, P, P, L, P, I, P, L, P]
         _configured = True
     return l
 
@@ -223,6 +223,27 @@ def depth_mix(x: torch.Tensor, history: torch.Tensor, n: int, coeffs: torch.Tens
     assert x.dtype == history.dtype == coeffs.dtype == torch.float32 and x.is_contiguous() and history.is_contiguous()
     assert history.shape[1:] == x.shape and history.shape[0] > n and coeffs.numel() == n + 1 and coeffs.is_contiguous()
     _check("depth_mix", lib().llmi_depth_mix(_ptr(x), _ptr(history), c_long(x.numel()), c_int(n), _ptr(coeffs), _stream()))
+
+
+def mix_layernorm(x: torch.Tensor, history: torch.Tensor, n: int, coeffs: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+                  eps: float, weight2: torch.Tensor | None = None, out2: torch.Tensor | None = None) -> bool:
+    """:func:`depth_mix` and, of the new x, :func:`layernorm` (one weight or two) in one kernel: the same x and history as
+    the two leave.  False (and nothing done) where the fused form does not apply: rows that are no whole 16-byte pieces,
+    widths over 4,096."""
+    _need_cuda(x, history, coeffs, weight, out, weight2, out2)
+    T, W = x.shape
+    assert x.dtype == history.dtype == coeffs.dtype == weight.dtype == torch.float32 and x.is_contiguous() and history.is_contiguous()
+    assert history.shape[1:] == x.shape and history.shape[0] > n and coeffs.numel() == n + 1 and coeffs.is_contiguous()
+    assert out.shape == (T, W) and out.is_contiguous() and weight.numel() == W and (weight2 is None) == (out2 is None)
+    if out2 is not None:
+        assert out2.shape == out.shape and out2.dtype == out.dtype and out2.is_contiguous() and weight2.dtype == torch.float32
+        assert weight2.numel() == W
+    rc = lib().llmi_mix_layernorm(c_int(_dtype_code(out)), _ptr(x), _ptr(history), c_int(n), _ptr(coeffs), _ptr(weight), _ptr(out),
+                                  _ptr(weight2), _ptr(out2), c_int(T), c_int(W), c_float(eps), _stream())
+    if rc == -5:          # not a size of the fused form
+        return False
+    _check("mix_layernorm", rc)
+    return True
 
 
 def gate_rows(a: torch.Tensor, z: torch.Tensor) -> None:
@@ -738,9 +759,10 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_
 PREFILL_SPLIT_PAGES = 16      # key pages per job when the prompt attention cuts its long query blocks
 
 
-def prefill_split_jobs(q_lens, kv_lens, window: int, split_pages: int) -> int:
+def prefill_split_jobs(q_lens, kv_lens, window: int, split_pages: int, pool: int = 0) -> int:
     """How many jobs the prompt attention has along its first grid dimension when every block of 128 queries
-    is cut into parts of ``split_pages`` key pages (the kernel's own rule, counted on the host)."""
+    is cut into parts of ``split_pages`` key pages (the kernel's own rule, counted on the host).  ``pool``: pages of
+    pooled rows (one per ``pool`` positions that lie before the window) come ahead of a block's own pages."""
     jobs = 0
     for q_len, kv_len in zip(q_lens, kv_lens):
         pos0 = kv_len - q_len
@@ -749,14 +771,19 @@ def prefill_split_jobs(q_lens, kv_lens, window: int, split_pages: int) -> int:
             last_q = first_q + min(128, q_len - mb * 128) - 1
             lo_key = first_q - window + 1 if (window > 0 and first_q - window + 1 > 0) else 0
             n_pg = last_q // 64 - lo_key // 64 + 1
+            if pool > 0 and last_q - window + 1 > 0:
+                n_pg += ((last_q - window + 1) // pool + 63) // 64
             jobs += (n_pg + split_pages - 1) // split_pages
     return jobs
 
 
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_q_start, seq_kv_len,
                          n_blocks: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0,
-                         split=None) -> None:
+                         split=None, pooled=None, gate=None) -> None:
     """The same prompt attention on the tcgen05 tensor cores (head size 64 or 128); arguments as ``attention_prefill``.
+    ``pooled = (pool, k_pool, v_pool, pool_pages)``: beside its window a query sees one pooled row per block of ``pool``
+    positions that lies wholly before the window (row b of the sequence's pooled pages is block b; caches shaped as the
+    token caches).  ``gate``: fp32 [tokens, >= n_heads]; head h's output is multiplied by logistic(gate[t, h]).
     ``split = (n_jobs, split_pages, workspace)``: cut the key range of every query block into jobs of
     ``split_pages`` pages (``n_jobs`` from :func:`prefill_split_jobs`, ``workspace`` fp32 of
     n_jobs * n_heads * (head_dim + 2) * 128 floats)."""
@@ -768,11 +795,22 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, s
     n_jobs, split_pages, ws = split if split is not None else (n_blocks, 0, None)
     if ws is not None:
         assert ws.dtype == torch.float32 and ws.is_cuda
+    pool, k_pool, v_pool, pool_pages = pooled if pooled is not None else (0, None, None, None)
+    if pool:
+        _need_cuda(k_pool, v_pool, pool_pages)
+        assert window > 0 and k_pool.dtype == v_pool.dtype == torch.bfloat16 and pool_pages.dtype == torch.int32
+        assert k_pool.is_contiguous() and v_pool.is_contiguous() and k_pool.shape[1:] == k_cache.shape[1:] == v_pool.shape[1:]
+        assert pool_pages.shape[0] == S and pool_pages.stride(1) == 1
+    if gate is not None:
+        _need_cuda(gate)
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == q.shape[0] and gate.shape[1] >= n_heads
     _check("attention_prefill_tc", lib().llmi_attention_prefill_tc(
         q.data_ptr(), q.stride(0), q.shape[0], out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
         k_cache.shape[0], seq_pages.data_ptr(), seq_pages.stride(0), seq_q_start.data_ptr(), seq_kv_len.data_ptr(), S,
         n_blocks, n_heads, n_kv_heads, head_dim, scale, window, n_jobs, split_pages, _addr(ws),
-        ws.numel() if ws is not None else 0, sc.attn_tickets.data_ptr(), sc.N_ATTN_TICKETS, sc.error.data_ptr(), _stream_int()))
+        ws.numel() if ws is not None else 0, sc.attn_tickets.data_ptr(), sc.N_ATTN_TICKETS, sc.error.data_ptr(), pool,
+        _addr(k_pool), _addr(v_pool), k_pool.shape[0] if pool else 0, _addr(pool_pages), pool_pages.stride(0) if pool else 0,
+        _addr(gate), gate.stride(0) if gate is not None else 0, _stream_int()))
 
 
 # Which prompt-attention kernel runs: "tc" (tcgen05: about 43 us for a 2,048-token prompt of 32 heads of 64) or
@@ -957,6 +995,27 @@ def attention_maps(q, out, k_cache, v_cache, ctx, seq_pages, page_size: int, n_h
     """The attention of a step in its general form (arguments as :func:`attention_flex`): bf16 sizes that the
     tensor-core kernel takes go there — prompts as blocks of 128 query rows, steps of single tokens cut over the
     positions (``rt`` lends the workspace of the cuts) —, everything else, and the 32-bit path, to the generic kernel."""
+    if (not ctx.decode and maps == 1 and chunk == 0 and head_scale is None and dk == dv and page_size == 64 and scale > 0
+            and q.dtype == out.dtype == k_cache.dtype == torch.bfloat16 and rt is not None and _MAPS_ATTENTION == "mma"
+            and _PREFILL_ATTENTION == "tc" and not _FORCE_GENERIC_ATTENTION and attention_prefill_tc_supported(dk)
+            and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+            and (pooled is None or not pooled[0] or window > 0)):
+        # one map, equal head sizes, no mask of chunks: the prompt kernel of the tcgen05 tensor cores (its window, the
+        # pooled rows ahead of it, the gate per head); key ranges are cut when the step has fewer jobs than the device SMs
+        pool = pooled[0] if pooled is not None else 0
+        split = None
+        q_lens, kv_lens = getattr(ctx, "host_q_lens", None), getattr(ctx, "host_kv_lens", None)
+        n_q_blocks = getattr(ctx, "n_q_blocks", None)
+        if not n_q_blocks:      # exact where the lengths are known (a cut key range counts its jobs from them), else an upper bound
+            n_q_blocks = sum((n + 127) // 128 for n in q_lens) if q_lens is not None else q.shape[0] // 128 + seq_pages.shape[0]
+        if _PREFILL_SPLIT and q_lens is not None and n_q_blocks * n_heads < sm_count():
+            jobs = prefill_split_jobs(q_lens, kv_lens, window, PREFILL_SPLIT_PAGES, pool)
+            if jobs > n_q_blocks:
+                ws = rt.scratch("attn_prefill_partials", (jobs * n_heads * (dk + 2) * 128,), torch.float32)
+                split = (jobs, PREFILL_SPLIT_PAGES, ws)
+        attention_prefill_tc(q, out, k_cache, v_cache, seq_pages, ctx.seq_q_start, ctx.seq_kv_len, n_q_blocks, n_heads,
+                             n_kv_heads, dk, scale, window, split, pooled if pool else None, gate)
+        return
     if (q.dtype == torch.bfloat16 and rt is not None and _MAPS_ATTENTION == "mma" and not _FORCE_GENERIC_ATTENTION
             and lib().llmi_attention_maps_mma_supported(c_int(dk), c_int(dv), c_int(n_heads // n_kv_heads), c_int(page_size))
             and q.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 8 == 0):
@@ -1343,9 +1402,10 @@ def moe_route(logits: torch.Tensor, top: int, ctx, idx: torch.Tensor, wt: torch.
                                              _stream()))
 
 
-def moe_experts_streamed(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int, a: torch.Tensor, y: torch.Tensor) -> None:
+def moe_experts_streamed(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int, a: torch.Tensor, y: torch.Tensor,
+                         add: bool = False) -> None:
     """y = sum over each token's choices of wt * down_e(act(gate_e h) * up_e h); the weight-streaming form.
-    w_gate, w_up [E, F, W], w_down [E, W, F] in h's type; a fp32 [T, top, F] scratch; y fp32 [T, W] (stored).
+    w_gate, w_up [E, F, W], w_down [E, W, F] in h's type; a fp32 [T, top, F] scratch; y fp32 [T, W] (stored, or with ``add`` added to).
     ``w_gate`` None: experts without a gate matrix, down_e(act(up_e h))."""
     _need_cuda(h, w_gate, w_up, w_down, idx, wt, a, y)
     T, W = h.shape
@@ -1358,7 +1418,7 @@ def moe_experts_streamed(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: in
     _check("moe_up", l.llmi_moe_up(c_int(_dtype_code(h)), _ptr(h), c_long(h.stride(0)), _ptr(w_gate), _ptr(w_up), c_int(W), c_int(F),
                                    c_int(top), _ptr(idx), _ptr(a), c_int(act), c_int(T), _stream()))
     _check("moe_down", l.llmi_moe_down(c_int(_dtype_code(h)), _ptr(a), _ptr(w_down), c_int(W), c_int(F), c_int(top), _ptr(idx),
-                                       _ptr(wt), _ptr(y), c_long(y.stride(0)), c_int(T), _stream()))
+                                       _ptr(wt), _ptr(y), c_long(y.stride(0)), c_int(T), c_int(1 if add else 0), _stream()))
 
 
 MOE_GROUPED_MIN_TOKENS = int(os.environ.get("LLMI_MOE_GROUPED_MIN", "4"))
@@ -1370,7 +1430,7 @@ def moe_grouped_applies(h: torch.Tensor, W: int, F: int, E: int) -> bool:
                 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0 and not _FORCE_SIMT)
 
 
-def moe_experts_grouped(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int, rt, y: torch.Tensor) -> None:
+def moe_experts_grouped(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int, rt, y: torch.Tensor, add: bool = False) -> None:
     """The same result as :func:`moe_experts_streamed` for many tokens: the (token, choice) items are grouped by expert
     and each expert's products run as tensor-core tiles over its rows.  bf16; ``rt`` lends the scratch."""
     _need_cuda(h, w_gate, w_up, w_down, idx, wt, y)
@@ -1387,4 +1447,4 @@ def moe_experts_grouped(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int
     _check("moe_grouped", lib().llmi_moe_grouped(
         _ptr(h), c_long(h.stride(0)), _ptr(w_gate), _ptr(w_up), _ptr(w_down), c_int(W), c_int(F), c_int(E), c_int(top), _ptr(idx),
         _ptr(wt), c_int(act), _ptr(scratch), c_long(n_int), _ptr(a_sorted), _ptr(y_sorted), _ptr(y), c_long(y.stride(0)), c_int(T),
-        _stream()))
+        c_int(1 if add else 0), _stream()))

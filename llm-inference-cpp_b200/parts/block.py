@@ -85,11 +85,19 @@ class ParallelBlock:
     def takes_padding_rows(self) -> bool:
         return True          # rows are treated alone
 
-    def forward(self, x, ctx, binding):
+    @property
+    def entry_norms(self):
+        """The norms this block applies to x first: whoever changes x last before the block may hand their outputs in
+        (``forward(..., entry=)``) — one tensor for a layer without a feed-forward, else a pair."""
+        return (self.mixer_norm,) if self.ffn is None else (self.mixer_norm, self.ffn_norm)
+
+    def forward(self, x, ctx, binding, entry=None):
         if self.ffn is None:
-            self.mixer.forward(self.mixer_norm.forward(x), x, ctx, binding)
+            self.mixer.forward(entry if entry is not None else self.mixer_norm.forward(x), x, ctx, binding)
             return
-        pair = self.mixer_norm.forward_pair(self.ffn_norm, x) if hasattr(self.mixer_norm, "forward_pair") else None
+        pair = entry
+        if pair is None and hasattr(self.mixer_norm, "forward_pair"):
+            pair = self.mixer_norm.forward_pair(self.ffn_norm, x)
         if pair is None:
             pair = (self.mixer_norm.forward(x, scratch_name="norm_out"), self.ffn_norm.forward(x, scratch_name="norm_out_b"))
         h1, h2 = pair

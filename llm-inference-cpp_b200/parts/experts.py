@@ -89,14 +89,11 @@ class RoutedExperts:
         idx = rt.scratch("router_choice", (T, self.top), torch.int32)
         wt = rt.scratch("router_weight", (T, self.top), torch.float32)
         kernels.moe_route(logits, self.top, ctx, idx, wt, self.route_mode, self.n_groups, self.keep, experts=self.E)
-        y = x if store else rt.scratch("experts_out", tuple(x.shape), torch.float32)
         if kernels.moe_grouped_applies(h, self.width, self.inner, self.E):
-            kernels.moe_experts_grouped(h, self.w_gate, self.w_up, self.w_down, idx, wt, self.act, rt, y)
+            kernels.moe_experts_grouped(h, self.w_gate, self.w_up, self.w_down, idx, wt, self.act, rt, x, add=not store)
         else:
             a = rt.scratch("experts_act", (T, self.top, self.inner), torch.float32)
-            kernels.moe_experts_streamed(h, self.w_gate, self.w_up, self.w_down, idx, wt, self.act, a, y)
-        if not store:
-            x += y
+            kernels.moe_experts_streamed(h, self.w_gate, self.w_up, self.w_down, idx, wt, self.act, a, x, add=not store)
         if self.shared:      # every token's expert: x += logistic(z_sg) * W_down act(W_up h); the gate scales the activation rows
             sa = rt.scratch("shared_act", (T, self.shared))
             kernels.linear(h, self.w_shared_up, sa, None, kernels.OUT_RELU2)

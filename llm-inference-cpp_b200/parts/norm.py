@@ -76,6 +76,18 @@ class LayerNorm:
         kernels.layernorm(x, self.weight, a, self.eps, None, other.weight, b)
         return a, b
 
+    def after_mix(self, other, x, history, n, coeffs, scratch_names=("norm_out", "norm_out_b")):
+        """The mixture over the depth (:func:`ops.kernels.depth_mix`) and, of the mixed x, this norm (with ``other``: a
+        second norm of this kind with the same eps) in one pass.  Returns the norms' outputs — one tensor, or a pair —,
+        or None with nothing done where the fused kernel does not apply."""
+        if other is not None and (type(other) is not LayerNorm or other.eps != self.eps or other.width != self.width):
+            return None
+        a = self.rt.scratch(scratch_names[0], (x.shape[0], self.width))
+        b = self.rt.scratch(scratch_names[1], (x.shape[0], self.width)) if other is not None else None
+        if not kernels.mix_layernorm(x, history, n, coeffs, self.weight, a, self.eps, other.weight if other is not None else None, b):
+            return None
+        return a if other is None else (a, b)
+
 
 @part("norm", "dyt")
 class DynamicTanh:

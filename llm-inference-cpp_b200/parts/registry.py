@@ -24,7 +24,9 @@ Families and what the engine calls on their members (``rt`` is the
 ``pass_exit``  ``forward(x, history, index, ctx)``: acts on the stream right behind scheduled call ``index``
                (``ScheduleEntry.after``); ``history`` fp32 ``[calls + 1, tokens, width]`` is the model's record of the
                step: row 0 the embedding output, row j + 1 the result of call j.  The part files the result of its call
-               (``history[index + 1] = x``) and may then rewrite ``x`` from the rows so far
+               (``history[index + 1] = x``) and may then rewrite ``x`` from the rows so far.  Where the next block names
+               the norms it applies first (``entry_norms``), the call comes with ``then=`` those norms; a part that makes
+               their outputs in its own pass returns them (the block takes them as ``entry``), else None
 ``conv``       ``cache_request() -> StateRequest | None`` and ``forward(h, ctx, binding) -> h'``: reshapes a sublayer's input
                over time (a short causal convolution) and keeps the inputs it still needs per sequence; ``binding`` is
                its own place in the cache (``CacheBinding.more[slot]`` of the call).  Any part of a layer other than the

@@ -372,7 +372,7 @@ def test_rotation_of_neighbours_and_values_from_keys(heads, kv, d, rot, dtype):
         assert np.abs(vc[pos // page, :, pos % page].float().cpu().numpy() - kr).max() < (1e-6 if dtype == "float32" else 2e-2)
 
 
-@pytest.mark.parametrize("E,top,groups", [(6, 2, (3, 2)), (12, 4, (2, 1)), (8, 3, None), (5, 5, None), (16, 2, (16, 3)), (64, 6, (8, 4)), (40, 1, (4, 4))])
+@pytest.mark.parametrize("E,top,groups", [(6, 2, (3, 2)), (12, 3, (2, 1)), (8, 3, None), (5, 5, None), (16, 2, (16, 3)), (64, 6, (8, 4)), (40, 1, (4, 4))])
 def test_experts_are_chosen_by_score_within_the_best_groups(E, top, groups):
     import torch
     from llmi_b200.ops import kernels
@@ -397,7 +397,7 @@ def test_experts_are_chosen_by_score_within_the_best_groups(E, top, groups):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("width", [20, 36, 128, 320, 2048, 2500, 4100])
+@pytest.mark.parametrize("width", [20, 36, 128, 260, 328, 2048, 2500, 4096, 4100])
 def test_layer_norm_alone_and_as_a_pair(width, dtype):
     import torch
     from llmi_b200.ops import kernels
@@ -437,3 +437,45 @@ def test_mixture_over_the_depth(shape):
         ref = sum(float(c[j]) * xs[j].astype(np.float64) for j in range(i + 2))
         assert np.abs(x.cpu().numpy() - ref).max() < 1e-5
         assert np.array_equal(hist[i + 1].cpu().numpy(), xs[i + 1])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [(5, 24), (3, 7), (9, 328), (64, 2048), (2, 4096), (3, 4100)])
+def test_mixture_over_the_depth_with_the_next_norms(shape, dtype):
+    """The mixture and the norms that read it next in one pass: the same stream and record as the mixture alone leaves
+    (to the bit), and the norms of that stream; sizes the fused form does not take fall back to the two kernels."""
+    import torch
+    from llmi_b200.engine.runtime import Runtime
+    import llmi_b200  # noqa: F401  (registers the parts)
+    from llmi_b200.parts.registry import get_part
+    from llmi_b200.parts.spec import PartSpec
+    dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    rt = Runtime(dt, "cuda:0")
+    T, W = shape
+    rng = np.random.default_rng(W)
+    w1, w2 = (rng.standard_normal(W).astype(np.float32) for _ in range(2))
+    norm_spec = PartSpec("layernorm", {"width": W, "eps": 1e-4, "tensor": ""}, "n")
+    norms = [get_part("norm", "layernorm")(norm_spec, {"": torch.tensor(w)}, rt) for w in (w1, w2)]
+    n_calls = 3
+    xs = [(rng.standard_normal(shape) * 2 + 5.0).astype(np.float32) for _ in range(n_calls + 1)]
+    hist_a = torch.full((n_calls + 1, T, W), float("nan"), device="cuda:0")
+    hist_b = hist_a.clone()
+    hist_a[0] = hist_b[0] = torch.tensor(xs[0], device="cuda:0")
+    tol = 1e-4 if dtype == "float32" else 8e-3
+    for i in range(n_calls):
+        c = rng.standard_normal(i + 2).astype(np.float32)
+        exit_ = get_part("pass_exit", "depth_average")(PartSpec("depth_average", {"index": i, "tensor": "dwa"}, "l."), {"dwa": torch.tensor(c)}, rt)
+        xa, xb = torch.tensor(xs[i + 1], device="cuda:0"), torch.tensor(xs[i + 1], device="cuda:0")
+        assert exit_.forward(xa, hist_a, i, None) is None
+        then = (norms[0], norms[1]) if i != 1 else (norms[0],)
+        done = exit_.forward(xb, hist_b, i, None, then=then)
+        assert torch.equal(xa, xb) and torch.equal(hist_a[i + 1], hist_b[i + 1])
+        mixed = xa.cpu().numpy().astype(np.float64)
+        if done is None:
+            assert W % 4 or W > 4096
+            continue
+        outs = done if isinstance(done, tuple) else (done,)
+        assert len(outs) == len(then)
+        for o, w in zip(outs, (w1, w2)):
+            ref = G.layer_norm(mixed, w, 1e-4)
+            assert (np.abs(o.float().cpu().numpy() - ref) / (1.0 + np.abs(ref))).max() < tol
