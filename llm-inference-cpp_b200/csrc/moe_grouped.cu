@@ -13,8 +13,12 @@
 // does not depend on its batch.  Needs W % 8 == 0 and F % 8 == 0 (16-byte rows); bf16 only.
 #include <math.h>
 
+#include <cuda.h>
+
 #include "common.cuh"
 #include "mma_sync.cuh"
+#include "sm100.cuh"
+#include "tc_common.cuh"
 
 namespace llmi {
 
@@ -26,7 +30,7 @@ constexpr int GB_SLOTS = GB_M * GB_CH / 128;   // pieces a thread copies per ope
 __global__ void __launch_bounds__(1024)
 moe_group_kernel(const int32_t* __restrict__ idx, int n_items, int E, int32_t* __restrict__ offsets,
                  int32_t* __restrict__ sorted_items, int32_t* __restrict__ item_pos, int32_t* __restrict__ tile_expert,
-                 int32_t* __restrict__ tile_row0, int32_t* __restrict__ n_tiles) {
+                 int32_t* __restrict__ tile_row0, int32_t* __restrict__ n_tiles, int tile_rows) {
   __shared__ int cnt[256], cursor[256];
   pdl_wait();
   pdl_launch_dependents();
@@ -42,7 +46,7 @@ moe_group_kernel(const int32_t* __restrict__ idx, int n_items, int E, int32_t* _
     for (int e = 0; e < E; ++e) {
       cursor[e] = run;
       offsets[e] = run;
-      for (int r = 0; r < cnt[e]; r += GB_M) {
+      for (int r = 0; r < cnt[e]; r += tile_rows) {
         tile_expert[tiles] = e;
         tile_row0[tiles] = run + r;
         ++tiles;
@@ -228,6 +232,210 @@ moe_combine_kernel(const float* __restrict__ ys, const int32_t* __restrict__ ite
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// The grouped products of many items on the 5th-generation tensor cores (tcgen05), for experts without a gate matrix.
+//
+// The items' input rows are first copied into the order of the grouping (moe_gather_rows_kernel), so that a tile of
+// 128 items of one expert is a box of a 2-d tensor map; the experts' weights [E, N, K] are a 3-d map whose boxes end
+// at an expert's last row.  The weight tile is the 128-row operand (out features on TMEM lanes), the item tile the N
+// operand (128 TMEM columns).  The grid is persistent over the units (item tile, weight-row tile), weight-row tiles
+// fastest: the CTAs that run at one time share an item tile and read an expert's weights once between them.  The
+// roles, the ring of stages and the two accumulators are those of the dense product (gemm_tc_kernel):
+//   warp 0 : cp.async.bulk.tensor of W [128 x 64] and items [128 x 64] into a ring of stages (128-byte swizzle)
+//   warp 1 : allocates TMEM; one thread issues tcgen05.mma (4 per stage) and tcgen05.commit
+//   warps 2..5 : tcgen05.ld the accumulator, apply the activation, store the rows of the tile that belong to its expert
+// A tile's rows past its expert's last item belong to the next expert (or to nobody): they are computed and not stored.
+// Every wait on an mbarrier is bounded (an error code in *error_flag, the CTA unwinds and frees its TMEM).
+constexpr int GT_BN = 128;
+constexpr int GT_STAGES = 6;
+constexpr int GT_A_BYTES = TC_BM * TC_BK * 2, GT_B_BYTES = GT_BN * TC_BK * 2, GT_STAGE_BYTES = GT_A_BYTES + GT_B_BYTES;
+constexpr int GT_SMEM = GT_STAGES * GT_STAGE_BYTES + 1024 + 8 * (2 * GT_STAGES + 4) + 16;
+constexpr int GT_TMEM_COLS = 2 * GT_BN;
+
+struct GtParams {
+  int N, K;                      // an expert's weight [N, K]
+  void* out;                     // [items, N], row pitch ldo: bf16 act(v) (mode 0) or fp32 v (mode 1)
+  long ldo;
+  int mode, act;                 // act 0: silu, 1: tanh GELU, 2: relu squared
+  const int32_t *offsets, *tile_expert, *tile_row0, *n_tiles;
+  int* error_flag;
+};
+
+__device__ __forceinline__ void tma_load_3d_box(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ h, long ldh, const int32_t* __restrict__ sorted_items,
+                       const int32_t* __restrict__ n_sorted, int top, int W, __nv_bfloat16* __restrict__ out) {
+  pdl_wait();
+  pdl_launch_dependents();
+  if ((int)blockIdx.x >= *n_sorted) return;      // items of no expert (rows of no sequence) are in no group
+  const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(sorted_items[blockIdx.x] / top) * ldh);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * W);
+  for (int i = threadIdx.x; i < W / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+__global__ void __launch_bounds__(TC_THREADS)
+moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GtParams p, int m_tiles) {
+  extern __shared__ uint8_t gt_smem_raw[];
+  const uint32_t base = (smem_u32(gt_smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + GT_STAGES * GT_STAGE_BYTES;   // full[S], empty[S], acc_full[2], acc_empty[2], tmem slot
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (GT_STAGES + s); };
+  auto acc_full = [&](int b) { return bars + 8u * (2 * GT_STAGES + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * GT_STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * GT_STAGES + 4);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kblocks = (p.K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    for (int s = 0; s < GT_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 4);   // the four epilogue warps
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)GT_TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  uint32_t tmem_d;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_d) : "r"(tmem_slot));
+
+  pdl_wait();                    // the tile lists, the item rows and the output belong to earlier kernels until now
+  pdl_launch_dependents();
+  const int n_units = *p.n_tiles * m_tiles;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+        const int t = u / m_tiles, mt = u - t * m_tiles;
+        const int e = p.tile_expert[t], row0 = p.tile_row0[t];
+        for (int i = 0; i < kblocks; ++i, ++it) {
+          const int s = it % GT_STAGES;
+          if (it >= GT_STAGES && !mbar_wait(empty_bar(s), ((it / GT_STAGES) - 1) & 1, p.error_flag, 21)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), GT_STAGE_BYTES);
+          const uint32_t a_dst = base + s * GT_STAGE_BYTES;
+          tma_load_3d_box(a_dst, &map_w, i * TC_BK, mt * TC_BM, e, full_bar(s));
+          tma_load_2d(a_dst + GT_A_BYTES, &map_x, i * TC_BK, row0, full_bar(s));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // instruction descriptor: D fp32, A and B bf16, both K-major, N = 128, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(GT_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++j) {
+        const int b = j & 1;
+        if (j >= 2 && !mbar_wait(acc_empty(b), ((j >> 1) - 1) & 1, p.error_flag, 24)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d_addr = tmem_d + (uint32_t)(b * GT_BN);
+        for (int i = 0; i < kblocks; ++i, ++it) {
+          const int s = it % GT_STAGES;
+          ok = mbar_wait(full_bar(s), (it / GT_STAGES) & 1, p.error_flag, 22);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = base + s * GT_STAGE_BYTES;
+          const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + GT_A_BYTES);
+#pragma unroll
+          for (int k4 = 0; k4 < TC_BK / 16; ++k4)
+            umma_bf16(d_addr, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+          umma_commit(empty_bar(s));
+        }
+        if (ok) umma_commit(acc_full(b));
+      }
+    }
+  } else {
+    const int quad = warp & 3;   // TMEM lane quadrant
+    int j = 0;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
+      const int t = u / m_tiles, mt = u - t * m_tiles;
+      const int e = p.tile_expert[t], row0 = p.tile_row0[t];
+      const int n_valid = min(GT_BN, p.offsets[e + 1] - row0);
+      const int b = j & 1;
+      const int m = mt * TC_BM + quad * 32 + lane;
+      const uint32_t t_base = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * GT_BN);
+      if (!mbar_wait(acc_full(b), (uint32_t)(j >> 1) & 1u, p.error_flag, 23)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      for (int c0 = 0; c0 < GT_BN; c0 += 16) {
+        float v[16];
+        tmem_ld16(t_base + c0, v);
+        const bool last = c0 + 16 >= GT_BN || c0 + 16 >= n_valid;
+        if (last) {              // the last read of this accumulator: hand it back
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty(b));
+        }
+        if (m < p.N) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            if (c0 + c >= n_valid) break;
+            const size_t idx = (size_t)(row0 + c0 + c) * p.ldo + m;
+            const float x = v[c];
+            if (p.mode == 1) {
+              ((float*)p.out)[idx] = x;
+            } else {
+              const float r = fmaxf(x, 0.f);
+              const float a = p.act == 2 ? r * r
+                              : p.act == 0 ? x / (1.0f + expf(-x))
+                                           : 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+              ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(a);
+            }
+          }
+        }
+        if (last) break;
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)GT_TMEM_COLS));
+  }
+}
+
+// A bf16 tensor map with 128-byte swizzle and boxes of [box_rows][64]: a matrix [rows, k] of row pitch ld (batch 0), or
+// `batch` such matrices one after another, contiguous (boxes of one matrix: rows past its last are filled with zeros).
+static int gt_make_map(CUtensorMap* map, const void* ptr, long k, long rows, long batch, long ld, int box_rows) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      return LLMI_ERR_DRIVER;
+    fn = (EncodeFn)sym;
+  }
+  const cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)(batch ? batch : 1)};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)rows * (cuuint64_t)ld * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows, 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, batch ? 3 : 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LLMI_OK : LLMI_ERR_DRIVER;
+}
+
 }  // namespace llmi
 
 using namespace llmi;
@@ -241,7 +449,8 @@ LLMI_EXPORT long llmi_moe_group_ints(int n_items, int E) {
 
 LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const void* wu, const void* wd, int W, int F, int E,
                                  int top, const int32_t* idx, const float* wt, int act, int32_t* scratch, long scratch_ints,
-                                 void* a_sorted, float* y_sorted, float* y, long ldy, int n_tokens, int add, cudaStream_t stream) {
+                                 void* a_sorted, float* y_sorted, float* y, long ldy, int n_tokens, int add, void* h_sorted,
+                                 int* error_flag, cudaStream_t stream) {
   if (n_tokens <= 0 || W <= 0 || F <= 0 || E <= 0 || E > 256 || top <= 0) return LLMI_ERR_BAD_SIZE;
   if ((W % 8) || (F % 8) || (ldh % 8) || ((uintptr_t)h & 15) || ((uintptr_t)wg & 15) || ((uintptr_t)wu & 15) || ((uintptr_t)wd & 15) ||
       ((uintptr_t)a_sorted & 15))
@@ -256,9 +465,46 @@ LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const 
   int32_t* tile_expert = item_pos + n_items;
   int32_t* tile_row0 = tile_expert + max_tiles;
   int32_t* n_tiles = tile_row0 + max_tiles;
+  // Many items of experts without a gate matrix, at sizes that fill 128 x 128 tiles: the tcgen05 kernel (h_sorted lends
+  // [n_items, W] bf16 for the items' input rows in the grouping's order).  LLMI_MOE_TC=0 keeps the mma.sync tiles.
+  static int tc_ok = -1;
+  if (tc_ok < 0) {
+    const char* ev = getenv("LLMI_MOE_TC");
+    tc_ok = (ev && ev[0] == '0') ? 0 : 1;
+  }
+  const bool tc = tc_ok && !wg && h_sorted && error_flag && n_items >= 1024 && W >= 128 && F >= 128 && !((uintptr_t)h_sorted & 15);
   int rc = launch_pdl(PDL_SMALL, moe_group_kernel, dim3(1), dim3(1024), 0, stream, idx, n_items, E, offsets, sorted_items, item_pos,
-                      tile_expert, tile_row0, n_tiles);
+                      tile_expert, tile_row0, n_tiles, tc ? GT_BN : GB_M);
   if (rc != LLMI_OK) return rc;
+  if (tc) {
+    CUtensorMap mw_up, mx_up, mw_down, mx_down;
+    if ((rc = gt_make_map(&mw_up, wu, W, F, E, W, TC_BM)) != LLMI_OK) return rc;
+    if ((rc = gt_make_map(&mx_up, h_sorted, W, n_items, 0, W, GT_BN)) != LLMI_OK) return rc;
+    if ((rc = gt_make_map(&mw_down, wd, F, W, E, F, TC_BM)) != LLMI_OK) return rc;
+    if ((rc = gt_make_map(&mx_down, a_sorted, F, n_items, 0, F, GT_BN)) != LLMI_OK) return rc;
+    static PerDevice<bool> tc_configured;
+    if (!tc_configured.here()) {
+      if (cudaFuncSetAttribute(moe_grouped_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GT_SMEM) != cudaSuccess)
+        return LLMI_ERR_LAUNCH;
+      tc_configured.here() = true;
+    }
+    rc = launch_pdl(PDL_SMALL, moe_gather_rows_kernel, dim3(n_items), dim3(256), 0, stream, (const __nv_bfloat16*)h, ldh,
+                    (const int32_t*)sorted_items, (const int32_t*)(offsets + E), top, W, (__nv_bfloat16*)h_sorted);
+    if (rc != LLMI_OK) return rc;
+    const int tiles_most = (n_items + GT_BN - 1) / GT_BN + E;
+    const int mt_up = (F + TC_BM - 1) / TC_BM, mt_down = (W + TC_BM - 1) / TC_BM;
+    GtParams pu{F, W, a_sorted, (long)F, 0, act, offsets, tile_expert, tile_row0, n_tiles, error_flag};
+    GtParams pd{W, F, (void*)y_sorted, (long)W, 1, 0, offsets, tile_expert, tile_row0, n_tiles, error_flag};
+    const long sms = sm_count();
+    rc = launch_pdl(PDL_GEMM, moe_grouped_tc_kernel, dim3((unsigned)min((long)tiles_most * mt_up, sms)), dim3(TC_THREADS), (size_t)GT_SMEM,
+                    stream, mw_up, mx_up, pu, mt_up);
+    if (rc != LLMI_OK) return rc;
+    rc = launch_pdl(PDL_GEMM, moe_grouped_tc_kernel, dim3((unsigned)min((long)tiles_most * mt_down, sms)), dim3(TC_THREADS),
+                    (size_t)GT_SMEM, stream, mw_down, mx_down, pd, mt_down);
+    if (rc != LLMI_OK) return rc;
+    return launch_pdl(PDL_SMALL, moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)y_sorted,
+                      (const int32_t*)item_pos, wt, top, W, y, ldy, add);
+  }
   const size_t smem_up = (size_t)GB_STAGES * 3 * GB_M * GB_LD * 2, smem_down = (size_t)GB_STAGES * 2 * GB_M * GB_LD * 2;
   const __nv_bfloat16* hb = (const __nv_bfloat16*)h;
   const __nv_bfloat16 *g = (const __nv_bfloat16*)wg, *u = (const __nv_bfloat16*)wu, *d = (const __nv_bfloat16*)wd;

@@ -1444,7 +1444,10 @@ def moe_experts_grouped(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int
     scratch = rt.scratch("experts_groups", (n_int,), torch.int32)
     a_sorted = rt.scratch("experts_act_sorted", (T * top, F), torch.bfloat16)
     y_sorted = rt.scratch("experts_out_sorted", (T * top, W), torch.float32)
+    # experts without a gate matrix take the tcgen05 tiles from 1,024 items on: those read the items' input rows in the
+    # grouping's order from a buffer of their own
+    h_sorted = rt.scratch("experts_in_sorted", (T * top, W), torch.bfloat16) if w_gate is None and T * top >= 1024 else None
     _check("moe_grouped", lib().llmi_moe_grouped(
         _ptr(h), c_long(h.stride(0)), _ptr(w_gate), _ptr(w_up), _ptr(w_down), c_int(W), c_int(F), c_int(E), c_int(top), _ptr(idx),
         _ptr(wt), c_int(act), _ptr(scratch), c_long(n_int), _ptr(a_sorted), _ptr(y_sorted), _ptr(y), c_long(y.stride(0)), c_int(T),
-        c_int(1 if add else 0), _stream()))
+        c_int(1 if add else 0), _ptr(h_sorted), _ptr(tc_scratch(h.device).error), _stream()))

@@ -396,6 +396,52 @@ def test_experts_are_chosen_by_score_within_the_best_groups(E, top, groups):
         assert np.abs(wt[t] - weights).max() < 1e-6
 
 
+@pytest.mark.parametrize("act", ["relu2", "silu"])
+@pytest.mark.parametrize("T,E,top,W,F", [(600, 4, 2, 128, 128), (1500, 8, 2, 256, 192), (520, 3, 2, 136, 200), (300, 12, 4, 384, 136),
+                                         (700, 5, 2, 64, 256), (2100, 16, 1, 192, 320)])
+def test_experts_without_a_gate_matrix_for_many_tokens(T, E, top, W, F, act):
+    """The grouped form for many (token, choice) items — from 1,024 items on and 128-wide sizes the tcgen05 tiles, else
+    the mma.sync tiles — against the sum written out in float64: experts with most of the items, with a few, with none;
+    sizes that end inside a tile in every direction; rows of no sequence get zeros."""
+    import torch
+    from llmi_b200.engine.runtime import Runtime
+    from llmi_b200.ops import kernels
+    rt = Runtime(torch.bfloat16, "cuda:0")
+    gen = torch.Generator(device="cuda:0").manual_seed(T + E)
+
+    def rnd(*shape, gain=1.0):
+        return (torch.randn(*shape, generator=gen, device="cuda:0") * gain).to(torch.bfloat16)
+    h, wu, wd = rnd(T, W), rnd(E, F, W, gain=W ** -0.5), rnd(E, W, F, gain=F ** -0.5)
+    # unequal loads: expert 0 is in most tokens' choices, the last expert in none
+    score = torch.rand(T, E, generator=gen, device="cuda:0")
+    score[:, 0] += 0.7
+    score[:, E - 1] = -1.0
+    idx = score.topk(top, dim=1).indices.to(torch.int32).contiguous()
+    wt = torch.rand(T, top, generator=gen, device="cuda:0")
+    idx[7] = -1
+    idx[T - 1] = -1
+    y = torch.full((T, W), float("nan"), device="cuda:0")
+    kernels.moe_experts_grouped(h, None, wu, wd, idx, wt, kernels.EXPERT_ACTIVATIONS[act], rt, y)
+    kernels.check_device_errors(torch.device("cuda:0"))
+    ref = torch.zeros(T, W, dtype=torch.float64, device="cuda:0")
+    hd = h.double()
+    for e in range(E):
+        for j in range(top):
+            rows = (idx[:, j] == e).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            z = hd[rows] @ wu[e].double().T
+            a = torch.relu(z) ** 2 if act == "relu2" else z * torch.sigmoid(z)
+            ref[rows] += wt[rows, j].double()[:, None] * (a @ wd[e].double().T)
+    assert torch.isfinite(y).all() and (y[7] == 0).all() and (y[T - 1] == 0).all()
+    err = (y.double() - ref).abs().max(dim=1).values / ref.abs().max()
+    assert float(err.max()) < 1.5e-2, (int(err.argmax()), float(err.max()))
+    # added to what is there, the same sum
+    y2 = torch.ones((T, W), device="cuda:0")
+    kernels.moe_experts_grouped(h, None, wu, wd, idx, wt, kernels.EXPERT_ACTIVATIONS[act], rt, y2, add=True)
+    assert float((y2 - 1.0 - y).abs().max()) < 1e-5 * max(1.0, float(y.abs().max()))
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("width", [20, 36, 128, 260, 328, 2048, 2500, 4096, 4100])
 def test_layer_norm_alone_and_as_a_pair(width, dtype):
