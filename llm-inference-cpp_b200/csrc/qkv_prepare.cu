@@ -158,12 +158,89 @@ qkv_prepare_heads_kernel(const float* __restrict__ proj, long ld, int n_q_heads,
                     k_cache, v_cache, q_out, ldq, t, hd);
 }
 
+// The same for many tokens with eight entries a thread (two 16-byte loads, one 16-byte store in bf16): neighbouring
+// pairs only (a chunk of eight holds four whole pairs), sizes in multiples of eight, the values being the keys or not.
+// Chunks are counted over the token's q heads, then its k heads, then its v heads; the arithmetic per entry is that of
+// prepare_part.
+template <typename T>
+__device__ __forceinline__ void store8(T* dst, const float* v);
+template <>
+__device__ __forceinline__ void store8<float>(float* dst, const float* v) {
+  reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const float* v) {
+  __nv_bfloat162 h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(h);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+qkv_prepare_chunks_kernel(const float* __restrict__ proj, long ld, int n_q_heads, int n_k_heads, int dk, int n_v_heads, int dv,
+                          const float* __restrict__ inv_freq, int rot_dims, float amplitude, int v_from_k,
+                          const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos, PagedKV kp, PagedKV vp,
+                          T* __restrict__ k_cache, T* __restrict__ v_cache, T* __restrict__ q_out, long ldq, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int seq = tok_seq[t];
+  const int cq = n_q_heads * dk / 8, ck = write_kv ? n_k_heads * dk / 8 : 0, cv = (write_kv && !v_from_k) ? n_v_heads * dv / 8 : 0;
+  const int pos = seq >= 0 ? tok_pos[t] : 0;
+  const float* row = proj + (size_t)t * ld;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < cq + ck + cv; c += gridDim.y * blockDim.x) {
+    float v[8];
+    if (seq < 0) {
+      if (c < cq) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        store8<T>(q_out + (size_t)t * ldq + (size_t)c * 8, v);
+      }
+      continue;
+    }
+    const float4 lo = reinterpret_cast<const float4*>(row + (size_t)c * 8)[0], hi = reinterpret_cast<const float4*>(row + (size_t)c * 8)[1];
+    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+    if (c >= cq + ck) {                                    // a chunk of a value head, as it is
+      const int e = (c - cq - ck) * 8, hd = e / dv;
+      store8<T>(v_cache + kv_row_offset(vp, seq, pos, hd) + (e - hd * dv), v);
+      continue;
+    }
+    const int e = (c < cq ? c : c - cq) * 8, hd = e / dk, e0 = e - hd * dk;      // entries e0 .. e0 + 7 of head hd
+    if (c >= cq && v_from_k) store8<T>(v_cache + kv_row_offset(vp, seq, pos, hd) + e0, v);   // the values: the keys before the rotation
+    if (e0 < rot_dims) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[e0 / 2 + i], &sn, &cs);
+        sn *= amplitude;
+        cs *= amplitude;
+        const float a = v[2 * i], b = v[2 * i + 1];
+        v[2 * i] = rot_lo(a, b, cs, sn);
+        v[2 * i + 1] = rot_hi(a, b, cs, sn);
+      }
+    }
+    T* dst = c < cq ? q_out + (size_t)t * ldq + (size_t)hd * dk + e0 : k_cache + kv_row_offset(kp, seq, pos, hd) + e0;
+    store8<T>(dst, v);
+  }
+}
+
+
 template <typename T>
 static int launch_prepare_heads(const float* proj, long ld, int n_q_heads, int n_k_heads, int dk, int n_v_heads, int dv,
                                 const float* inv_freq, int rot_dims, int pairing, float amplitude, int v_from_k,
                                 const int32_t* tok_seq, const int32_t* tok_pos, PagedKV kp, PagedKV vp, void* k_cache, void* v_cache,
                                 void* q_out, long ldq, int n_tokens, bool kv, cudaStream_t stream) {
   const int heads = n_q_heads + (kv ? n_k_heads + (v_from_k ? 0 : n_v_heads) : 0);
+  // many tokens, neighbouring pairs (or no rotation), everything in multiples of eight entries and 16 bytes: eight entries a thread
+  if (n_tokens > 128 && (pairing || rot_dims == 0) && !(dk % 8) && !(dv % 8) && !(rot_dims % 8) && !(ld % 4) && !(ldq % 8) &&
+      !((uintptr_t)proj & 15) && !((uintptr_t)q_out & 15) && !((uintptr_t)k_cache & 15) && !((uintptr_t)v_cache & 15)) {
+    const int chunks = (n_q_heads * dk + (kv ? n_k_heads * dk + (v_from_k ? 0 : n_v_heads * dv) : 0)) / 8;
+    return launch_pdl(PDL_SMALL, qkv_prepare_chunks_kernel<T>, dim3(n_tokens, (chunks + 255) / 256), dim3(128), 0, stream, proj, ld,
+                      n_q_heads, n_k_heads, dk, n_v_heads, dv, inv_freq, rot_dims, amplitude, v_from_k, tok_seq, tok_pos, kp, vp,
+                      (T*)k_cache, (T*)v_cache, (T*)q_out, ldq, kv ? 1 : 0);
+  }
   // few tokens: a head per block of 64 threads; many: four heads per block of 128 (fewer, longer blocks)
   const int per = n_tokens <= 128 ? 1 : 4, threads = n_tokens <= 128 ? 64 : 128;
   return launch_pdl(PDL_SMALL, qkv_prepare_heads_kernel<T>, dim3(n_tokens, (heads + per - 1) / per), dim3(threads), 0, stream, proj, ld,

@@ -340,18 +340,21 @@ def test_attention_sees_its_window_and_the_blocks_before_it(window, pool, key, s
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,kv,d,rot", [(2, 1, 8, 8), (3, 3, 12, 6), (4, 2, 64, 32), (2, 2, 10, 0)])
-def test_rotation_of_neighbours_and_values_from_keys(heads, kv, d, rot, dtype):
+@pytest.mark.parametrize("T,extra", [(9, 5), (150, 4)])
+@pytest.mark.parametrize("heads,kv,d,rot", [(2, 1, 8, 8), (3, 3, 12, 6), (4, 2, 64, 32), (2, 2, 10, 0), (5, 1, 128, 64), (2, 2, 16, 0)])
+def test_rotation_of_neighbours_and_values_from_keys(heads, kv, d, rot, dtype, T, extra):
     """qkv_prepare with neighbouring pairs, an amplitude on cos and sin, and values that are the keys before the
-    rotation, against the plain rotation; positions up to a few thousand."""
+    rotation, against the plain rotation; positions up to a few thousand.  Few tokens take the kernel of one entry a
+    thread; many tokens with sizes in multiples of eight (and rows of whole 16 bytes: ``extra`` columns behind the
+    keys) the one of eight entries a thread."""
     import torch
     from llmi_b200.ops import kernels
     dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
     rng = np.random.default_rng(d + rot)
-    T, page, first = 9, 64, 3000
+    page, first = 64, 3000
     rot_cfg = {"dims": rot, "base": 500.0, "scaling": {"factor": 6.0, "original": 40, "fast": 4.0, "slow": 0.5}}
     f, mult = G.rotation_frequencies(rot_cfg) if rot else (np.zeros(0), 1.0)
-    proj = torch.tensor(rng.standard_normal((T, (heads + kv) * d + 5)).astype(np.float32), device="cuda:0")
+    proj = torch.tensor(rng.standard_normal((T, (heads + kv) * d + extra)).astype(np.float32), device="cuda:0")
     n_pages = (first + T) // page + 1
     pages = torch.arange(n_pages, dtype=torch.int32, device="cuda:0")[None, :].contiguous()
     kc = torch.zeros((n_pages, kv, page, d), dtype=dt, device="cuda:0")
