@@ -60,7 +60,12 @@ WIDE = config(128, 300, [(att(4, 2, 64, window=100, pool=16, rot_dims=32, scalin
 # sizes that fit no fast kernel: rows of odd byte counts, head counts that divide nothing
 ODD = config(36, 77, [(att(5, 5, 6, window=11, pool=4, rot_dims=2, base=50.0), moe(10, 3, 2, shared=7)),
                       (att(3, 1, 10, window=6, pool=9, rot_dims=6, scaling=(5.0, 8, 2.0, 0.25)), dense(22))], eps=1e-6)
-CONFIGS = {"odd": ODD, "window_pool": WINDOW_POOL, "window": WINDOW_ONLY, "no_mask": NO_MASK, "dense": DENSE, "experts": EXPERTS,
+# heads larger than the tensor-core kernels' 64 and 128, and between them
+BIG_HEADS = config(192, 211, [(att(2, 1, 96, window=50, pool=6, rot_dims=48, scaling=(4.0, 64, 16.0, 1.0)), dense(128)),
+                              (att(2, 2, 160, window=70, pool=9, rot_dims=160), moe(128, 6, 2, groups=(3, 2), shared=64)),
+                              (att(3, 1, 192, window=33, pool=4, rot_dims=64), None),
+                              (att(2, 1, 256, window=90, pool=16, rot_dims=128, scaling=(8.0, 32, 8.0, 1.0)), moe(256, 4, 2))])
+CONFIGS = {"big_heads": BIG_HEADS, "odd": ODD, "window_pool": WINDOW_POOL, "window": WINDOW_ONLY, "no_mask": NO_MASK, "dense": DENSE, "experts": EXPERTS,
            "mixed": MIXED, "wide": WIDE}
 
 
