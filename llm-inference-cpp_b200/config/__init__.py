@@ -2,5 +2,6 @@
 from .garodra import GarodraConfig  # noqa: F401
 from .gemosun import GemosunConfig  # noqa: F401
 from .llama import ConfigError, LlamaConfig  # noqa: F401
+from .renitar import RenitarConfig  # noqa: F401
 from .registry import (Architecture, get_architecture, parse_config, read_model_config,  # noqa: F401
                        register_architecture, registered_architectures)

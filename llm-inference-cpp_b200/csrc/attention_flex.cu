@@ -4,11 +4,13 @@
 //     SAME values; the output is [head][map][dv], one softmax-weighted sum per map (what a differential
 //     attention then subtracts: llmi_diff_combine);
 //   * query head h reads kv head h / (heads / kv_heads);
-//   * score = (q . k) * scale * head_scale[h]  (head_scale optional);
+//   * score = (q . k) * scale * head_scale[h]  (head_scale optional); with softcap > 0 the score then passes
+//     softcap * tanh(score / softcap);
 //   * the keys a query at position p sees: max(p - window + 1, floor(p / chunk) * chunk, 0) .. p
 //     (window 0: no window; chunk 0: no chunks) — chunks are counted from position 0 of the sequence;
 //   * optionally, beside a window, one pooled key and value per block of positions that lies wholly before it
-//     (PooledKV below), in the same softmax, and a logistic gate per (token, head) on the output.
+//     (PooledKV below), in the same softmax, and a logistic gate on the output: one number per (token, head), or one
+//     per output entry.
 // One warp owns one (token, head, map).  Keys are taken 32 at a time in blocks anchored at absolute positions
 // 0, 32, 64, ... with a running maximum and sum, so the order of every addition depends on the key's position only,
 // not on how the step was cut or batched.  Serves prompts and single tokens of the fp32 path, and bf16 sizes that
@@ -73,13 +75,16 @@ __device__ __forceinline__ float flex_dot<float>(const float* __restrict__ q, co
 template <typename T, int NJ>
 __device__ __forceinline__ void flex_run(const float* __restrict__ q_s, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                                          const PagedKV& kp, const PagedKV& vp, int seq, int kh, int kvh, int lo, int hi, float sc,
-                                         int lane, float& m, float& l, float (&acc)[NJ]) {
+                                         float softcap, int lane, float& m, float& l, float (&acc)[NJ]) {
   const int dk = kp.head_dim, dv = vp.head_dim;
   for (int c0 = (lo / 32) * 32; c0 <= hi; c0 += 32) {
     const int s = c0 + lane;
     const bool valid = s >= lo && s <= hi;
     float score = -INFINITY;
-    if (valid) score = flex_dot<T>(q_s, k_cache + kv_row_offset(kp, seq, s, kh), dk) * sc;
+    if (valid) {
+      score = flex_dot<T>(q_s, k_cache + kv_row_offset(kp, seq, s, kh), dk) * sc;
+      if (softcap > 0.f) score = softcap * tanhf(score / softcap);
+    }
     const float m_new = fmaxf(m, warp_max(score));
     const float p = valid ? expf(score - m_new) : 0.f;
     const float corr = expf(m - m_new);  // first block: exp(-inf) = 0
@@ -115,15 +120,16 @@ __host__ __device__ __forceinline__ int pooled_blocks_visible(int pos, int windo
   return (pool > 0 && window > 0 && pos - window + 1 > 0) ? (pos - window + 1) / pool : 0;
 }
 
-// NJ = ceil(dv / 32): output elements per lane.  OutT: the compute type, or float.  `gate` (optional, fp32, one
-// number per (token, head) at gate[t * ldg + h]): the head's output is multiplied by its logistic function.
+// NJ = ceil(dv / 32): output elements per lane.  OutT: the compute type, or float.  `gate` (optional, fp32): the
+// output is multiplied by the logistic function of one number per (token, head) at gate[t * ldg + h] (gate_per 1) or of
+// one number per output entry at gate[t * ldg + h * dv + d] (gate_per = dv).
 template <typename T, typename OutT, int NJ>
 __global__ void __launch_bounds__(FLEX_WARPS * 32)
 attention_flex_kernel(const T* __restrict__ q, long ldq, OutT* __restrict__ out, long ldo, const T* __restrict__ k_cache,
                       const T* __restrict__ v_cache, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos,
                       PagedKV kp, PagedKV vp, int n_tokens, int n_heads, int maps, float scale,
                       const float* __restrict__ head_scale, int window, int chunk, PooledKV pooled,
-                      const float* __restrict__ gate, long ldg) {
+                      const float* __restrict__ gate, long ldg, int gate_per, float softcap) {
   __shared__ float q_s[FLEX_WARPS][FLEX_MAX_DK];
   pdl_launch_dependents();
   pdl_wait();
@@ -157,14 +163,17 @@ attention_flex_kernel(const T* __restrict__ q, long ldq, OutT* __restrict__ out,
 
   const int nb = pooled.k ? pooled_blocks_visible(pos, window, pooled.pool) : 0;
   if (nb > 0)
-    flex_run<T, NJ>(q_s[warp], (const T*)pooled.k, (const T*)pooled.v, pooled.kp, pooled.vp, seq, kh, kvh, 0, nb - 1, sc, lane, m, l, acc);
-  flex_run<T, NJ>(q_s[warp], k_cache, v_cache, kp, vp, seq, kh, kvh, lo, pos, sc, lane, m, l, acc);
+    flex_run<T, NJ>(q_s[warp], (const T*)pooled.k, (const T*)pooled.v, pooled.kp, pooled.vp, seq, kh, kvh, 0, nb - 1, sc, softcap, lane, m, l, acc);
+  flex_run<T, NJ>(q_s[warp], k_cache, v_cache, kp, vp, seq, kh, kvh, lo, pos, sc, softcap, lane, m, l, acc);
   float inv = 1.0f / l;
-  if (gate) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h]));
+  if (gate && gate_per <= 1) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + h]));
 #pragma unroll
   for (int j = 0; j < NJ; ++j) {
     const int d = lane + 32 * j;
-    if (d < dv) o[d] = from_f32<OutT>(acc[j] * inv);
+    if (d >= dv) continue;
+    float r = acc[j] * inv;
+    if (gate && gate_per > 1) r *= 1.0f / (1.0f + expf(-gate[(size_t)t * ldg + (size_t)h * dv + d]));
+    o[d] = from_f32<OutT>(r);
   }
 }
 
@@ -247,7 +256,7 @@ template <typename T, typename OutT>
 int launch_attention_flex(const void* q, long ldq, void* out, long ldo, const void* k_cache, const void* v_cache,
                           const int32_t* tok_seq, const int32_t* tok_pos, PagedKV kp, PagedKV vp, int n_tokens, int n_heads,
                           int maps, float scale, const float* head_scale, int window, int chunk, PooledKV pooled,
-                          const float* gate, long ldg, cudaStream_t stream) {
+                          const float* gate, long ldg, int gate_per, float softcap, cudaStream_t stream) {
   const long items = (long)n_tokens * n_heads * maps;
   const long blocks = (items + FLEX_WARPS - 1) / FLEX_WARPS;
   if (blocks > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
@@ -255,7 +264,7 @@ int launch_attention_flex(const void* q, long ldq, void* out, long ldo, const vo
 #define LLMI_LAUNCH(NJ)                                                                                                  \
   return launch_pdl(PDL_ATTENTION, attention_flex_kernel<T, OutT, NJ>, dim3((unsigned)blocks), dim3(FLEX_WARPS * 32), 0, \
                     stream, (const T*)q, ldq, (OutT*)out, ldo, (const T*)k_cache, (const T*)v_cache, tok_seq, tok_pos,   \
-                    kp, vp, n_tokens, n_heads, maps, scale, head_scale, window, chunk, pooled, gate, ldg)
+                    kp, vp, n_tokens, n_heads, maps, scale, head_scale, window, chunk, pooled, gate, ldg, gate_per, softcap)
   if (nj <= 1) LLMI_LAUNCH(1);
   if (nj <= 2) LLMI_LAUNCH(2);
   if (nj <= 4) LLMI_LAUNCH(4);
@@ -302,15 +311,18 @@ LLMI_EXPORT int llmi_attention_flex(int dtype, const void* q, long ldq, void* ou
                                     const int32_t* seq_pages, int pages_stride, int page_size, int n_tokens, int n_heads,
                                     int n_kv_heads, int maps, int dk, int dv, float scale, const float* head_scale, int window,
                                     int chunk, int pool, const void* k_pool, const void* v_pool, const int32_t* pool_pages,
-                                    int pool_pages_stride, const float* gate, long ldg, cudaStream_t stream) {
+                                    int pool_pages_stride, const float* gate, long ldg, int gate_per, float softcap,
+                                    cudaStream_t stream) {
   if (n_tokens <= 0 || n_heads <= 0 || n_kv_heads <= 0 || maps <= 0 || dk <= 0 || dv <= 0 || page_size <= 0) return LLMI_ERR_BAD_SIZE;
+  if (gate && gate_per != 1 && (gate_per != dv || maps != 1)) return LLMI_ERR_UNSUPPORTED;
+  if (softcap < 0.f) return LLMI_ERR_BAD_SIZE;
   if (dk > FLEX_MAX_DK || dv > FLEX_MAX_DV || n_heads % n_kv_heads != 0 || window < 0 || chunk < 0) return LLMI_ERR_BAD_SIZE;
   if (pool < 0 || (pool > 0 && (!k_pool || !v_pool || !pool_pages || window <= 0))) return LLMI_ERR_BAD_SIZE;
   const PagedKV kp{seq_pages, pages_stride, page_size, n_kv_heads * maps, dk}, vp{seq_pages, pages_stride, page_size, n_kv_heads, dv};
   PooledKV pooled{pool > 0 ? k_pool : nullptr, pool > 0 ? v_pool : nullptr,
                   PagedKV{pool_pages, pool_pages_stride, page_size, n_kv_heads * maps, dk},
                   PagedKV{pool_pages, pool_pages_stride, page_size, n_kv_heads, dv}, pool};
-#define LLMI_ARGS q, ldq, out, ldo, k_cache, v_cache, tok_seq, tok_pos, kp, vp, n_tokens, n_heads, maps, scale, head_scale, window, chunk, pooled, gate, ldg, stream
+#define LLMI_ARGS q, ldq, out, ldo, k_cache, v_cache, tok_seq, tok_pos, kp, vp, n_tokens, n_heads, maps, scale, head_scale, window, chunk, pooled, gate, ldg, gate_per, softcap, stream
   if (dtype == LLMI_DTYPE_F32) return launch_attention_flex<float, float>(LLMI_ARGS);
   if (dtype == LLMI_DTYPE_BF16)
     return out_f32 ? launch_attention_flex<__nv_bfloat16, float>(LLMI_ARGS) : launch_attention_flex<__nv_bfloat16, __nv_bfloat16>(LLMI_ARGS);

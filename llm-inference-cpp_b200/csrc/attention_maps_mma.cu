@@ -21,7 +21,8 @@
 // Optionally (pool > 0, beside a window) a query also sees one pooled key and value per block of `pool` positions that
 // lies wholly before its window: rows of pages of their own (one row per block), walked as further 64-row tiles AHEAD of
 // the window's pages in the same loop and the same running softmax; and optionally every head's output is multiplied by
-// the logistic function of a number per (token, head).
+// the logistic function of a number per (token, head), or every output entry by that of a number of its own; and
+// optionally (softcap > 0) a score passes softcap * tanh(score / softcap) before the softmax.
 // The order of every addition depends on positions only (pages anchored at multiples of 64, parts by key index), not
 // on the batch; cuts follow the page table's width, which is part of a recorded step's shape.
 #include <math.h>
@@ -67,14 +68,22 @@ struct MapsArgs {
   int pool_pages_stride;
   const float* gate;            // [T, ldg]: head h's output times logistic(gate[t * ldg + h]); null: none
   long ldg;
+  int gate_per;                 // 1: a number per head; dv: a number per output entry, at gate[t * ldg + h * dv + d] (one map)
+  float softcap_log2;           // softcap * log2(e); 0: scores are not capped
 };
 
 __device__ __forceinline__ int maps_pooled_visible(int pos, int window, int pool) {
   return (pool > 0 && window > 0 && pos - window + 1 > 0) ? (pos - window + 1) / pool : 0;
 }
 __device__ __forceinline__ float maps_gate(const MapsArgs& a, int t, int head) {
-  return a.gate ? 1.0f / (1.0f + __expf(-a.gate[(size_t)t * a.ldg + head])) : 1.0f;
+  return (a.gate && a.gate_per <= 1) ? 1.0f / (1.0f + __expf(-a.gate[(size_t)t * a.ldg + head])) : 1.0f;
 }
+// the gate of one output entry (1 where the gate is a number per head: maps_gate has it)
+__device__ __forceinline__ float maps_gate_entry(const MapsArgs& a, int t, int head, int dv, int d) {
+  return (a.gate && a.gate_per > 1) ? 1.0f / (1.0f + __expf(-a.gate[(size_t)t * a.ldg + (size_t)head * dv + d])) : 1.0f;
+}
+// tanh on the exponential unit: 1 - 2 / (1 + e^(2x)); x is a score over its cap, the result ends up in a bf16 weight
+__device__ __forceinline__ float maps_tanh(float x) { return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x)); }
 
 // NV = dv / 16.  PROMPT: the form (see above).
 template <int NV, bool PROMPT>
@@ -213,6 +222,7 @@ attention_maps_mma_kernel(const MapsArgs a) {
     cp_async_commit();
   };
 
+  const float inv_cap = a.softcap_log2 > 0.f ? 1.0f / a.softcap_log2 : 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   float o[2 * NV][4];
 #pragma unroll
@@ -266,7 +276,8 @@ attention_maps_mma_kernel(const MapsArgs a) {
       for (int e = 0; e < 4; ++e) {
         const int key = base + 8 * j + 2 * tq + (e & 1), i = e >> 1;
         const bool seen = pooled ? key < row_nb[i] : (key <= row_pos[i] && key >= row_lo[i]);
-        const float v = seen ? s[j][e] * row_scale[i] : -INFINITY;
+        float v = seen ? s[j][e] * row_scale[i] : -INFINITY;
+        if (a.softcap_log2 > 0.f && seen) v = a.softcap_log2 * maps_tanh(v * inv_cap);
         s[j][e] = v;
         mx[i] = fmaxf(mx[i], v);
       }
@@ -325,8 +336,10 @@ attention_maps_mma_kernel(const MapsArgs a) {
       const size_t at = (size_t)t * a.ldo + (size_t)(head0 * a.maps + mp) * DV + 2 * tq;
 #pragma unroll
       for (int j = 0; j < 2 * NV; ++j) {
-        if (a.out_f32) *reinterpret_cast<float2*>((float*)a.out + at + 8 * j) = make_float2(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
-        else *reinterpret_cast<__nv_bfloat162*>((__nv_bfloat16*)a.out + at + 8 * j) = __floats2bfloat162_rn(o[j][2 * i] * inv, o[j][2 * i + 1] * inv);
+        const float r0 = o[j][2 * i] * inv * maps_gate_entry(a, t, head0, DV, 8 * j + 2 * tq);
+        const float r1 = o[j][2 * i + 1] * inv * maps_gate_entry(a, t, head0, DV, 8 * j + 2 * tq + 1);
+        if (a.out_f32) *reinterpret_cast<float2*>((float*)a.out + at + 8 * j) = make_float2(r0, r1);
+        else *reinterpret_cast<__nv_bfloat162*>((__nv_bfloat16*)a.out + at + 8 * j) = __floats2bfloat162_rn(r0, r1);
       }
     }
   }
@@ -363,7 +376,7 @@ attention_maps_mma_kernel(const MapsArgs a) {
       const size_t hm = (size_t)(head0 + r) * a.maps + mp;
       if (a.splits == 1) {
         const size_t at = (size_t)t0 * a.ldo + hm * DV + c;
-        const float res = acc / l * maps_gate(a, t0, head0 + r);
+        const float res = acc / l * maps_gate(a, t0, head0 + r) * maps_gate_entry(a, t0, head0 + r, DV, c);
         if (a.out_f32) ((float*)a.out)[at] = res;
         else ((__nv_bfloat16*)a.out)[at] = __float2bfloat16_rn(res);
       } else {
@@ -383,7 +396,7 @@ constexpr int AM_MAX_PARTS = 1024;
 __global__ void __launch_bounds__(128)
 attention_maps_join_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, void* __restrict__ out, long ldo,
                            int out_f32, const int32_t* __restrict__ tok_seq, int per_tok, int dv, int parts,
-                           const float* __restrict__ gate, long ldg, int maps) {
+                           const float* __restrict__ gate, long ldg, int maps, int gate_per) {
   __shared__ float w_s[AM_MAX_PARTS];
   __shared__ float red[32];
   pdl_wait();
@@ -409,14 +422,16 @@ attention_maps_join_kernel(const float* __restrict__ ws_o, const float* __restri
     part += w * ml[2 * s + 1];
   }
   float inv = 1.0f / block_sum(part, red);
-  if (gate) inv *= 1.0f / (1.0f + __expf(-gate[(size_t)t * ldg + hm / maps]));
+  if (gate && gate_per <= 1) inv *= 1.0f / (1.0f + __expf(-gate[(size_t)t * ldg + hm / maps]));
   const float* o = ws_o + (size_t)item * parts * dv;
   for (int c = threadIdx.x; c < dv; c += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < parts; ++s)
       if (w_s[s] != 0.f) acc = fmaf(w_s[s], o[(size_t)s * dv + c], acc);      // (a part that saw no key holds nothing)
-    if (out_f32) ((float*)out)[at + c] = acc * inv;
-    else ((__nv_bfloat16*)out)[at + c] = __float2bfloat16_rn(acc * inv);
+    float res = acc * inv;
+    if (gate && gate_per > 1) res *= 1.0f / (1.0f + __expf(-gate[(size_t)t * ldg + (size_t)hm * dv + c]));
+    if (out_f32) ((float*)out)[at + c] = res;
+    else ((__nv_bfloat16*)out)[at + c] = __float2bfloat16_rn(res);
   }
 }
 
@@ -456,7 +471,10 @@ LLMI_EXPORT int llmi_attention_maps_mma(const void* q, long ldq, void* out, long
                                         int dk, int dv, float scale, const float* head_scale, int window, int chunk, int prompt,
                                         int n_blocks, int splits, int pages_per_split, float* workspace, long workspace_floats,
                                         int pool, const void* k_pool, const void* v_pool, const int32_t* pool_pages,
-                                        int pool_pages_stride, const float* gate, long ldg, cudaStream_t stream) {
+                                        int pool_pages_stride, const float* gate, long ldg, int gate_per, float softcap,
+                                        cudaStream_t stream) {
+  if (gate && gate_per != 1 && (gate_per != dv || maps != 1)) return LLMI_ERR_UNSUPPORTED;
+  if (softcap < 0.f) return LLMI_ERR_BAD_SIZE;
   if (n_tokens <= 0 || n_seqs <= 0 || n_heads <= 0 || n_kv_heads <= 0 || maps <= 0 || n_heads % n_kv_heads) return LLMI_ERR_BAD_SIZE;
   if (!llmi_attention_maps_mma_supported(dk, dv, n_heads / n_kv_heads, AM_PAGE)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || (ldq % 8) || ((uintptr_t)out & 7) || (ldo % 2))
@@ -473,6 +491,7 @@ LLMI_EXPORT int llmi_attention_maps_mma(const void* q, long ldq, void* out, long
     return LLMI_ERR_BAD_SIZE;
   a.pool = pool; a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
   a.pool_pages = pool_pages; a.pool_pages_stride = pool_pages_stride; a.gate = gate; a.ldg = ldg;
+  a.gate_per = gate_per; a.softcap_log2 = softcap * 1.4426950408889634f;
   const int rows = prompt ? AM_PROMPT_ROWS : 16;
   const int nbuf = prompt ? 2 : AM_TOKEN_BUFFERS;
   const size_t smem = ((size_t)(rows + nbuf * AM_PAGE) * (dk + AM_PAD) + (size_t)nbuf * AM_PAGE * (dv + AM_PAD)) * 2;
@@ -500,5 +519,5 @@ LLMI_EXPORT int llmi_attention_maps_mma(const void* q, long ldq, void* out, long
   const long items = (long)n_tokens * n_heads * maps;
   if (items > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
   return launch_pdl(PDL_SMALL, attention_maps_join_kernel, dim3((unsigned)items), dim3(128), 0, stream, (const float*)a.ws_o,
-                    (const float*)a.ws_ml, out, ldo, out_f32, tok_seq, n_heads * maps, dv, splits, gate, ldg, maps);
+                    (const float*)a.ws_ml, out, ldo, out_f32, tok_seq, n_heads * maps, dv, splits, gate, ldg, maps, gate_per);
 }

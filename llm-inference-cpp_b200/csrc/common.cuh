@@ -80,13 +80,29 @@ constexpr int OUT_GEGLU_REQUEST = 4;
 // and mode 5: a plain store (bias added) through the square of relu (the launchers turn it into OUT_STORE with `act` = 2).
 constexpr int OUT_RELU2_REQUEST = 5;
 constexpr int ACT_STORE_RELU2 = 2;
-// What a storing epilogue writes for the value v (bias added): v, or relu(v)^2 when `act` says so.
+// and mode 6: a plain store (bias added) through the exact GELU, v * Phi(v) (OUT_STORE with `act` = 3).
+constexpr int OUT_GELU_REQUEST = 6;
+constexpr int ACT_STORE_GELU = 3;
+// What a storing epilogue writes for the value v (bias added): v, relu(v)^2 or 0.5 v (1 + erf(v / sqrt(2))) as `act` says.
 __device__ __forceinline__ float stored_value(float v, int act) {
   if (act == ACT_STORE_RELU2) {
     v = fmaxf(v, 0.f);
     return v * v;
   }
+  if (act == ACT_STORE_GELU) return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
   return v;
+}
+// The activation of a storing mode (0: none).
+__host__ __device__ __forceinline__ int store_act_of(int mode) {
+  return mode == OUT_RELU2_REQUEST ? ACT_STORE_RELU2 : (mode == OUT_GELU_REQUEST ? ACT_STORE_GELU : 0);
+}
+
+// The activation of a routed expert.  act 0: silu; 1: the tanh form of GELU; 2: relu squared; 3: the exact GELU.
+__device__ __forceinline__ float expert_act(float v, int act) {
+  if (act == 0) return v / (1.0f + expf(-v));
+  if (act == 2) { v = fmaxf(v, 0.f); return v * v; }
+  if (act == 3) return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
+  return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
 }
 
 // act(gate) * up of the gated epilogues.  act 0: silu; 1: 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).  The

@@ -349,10 +349,10 @@ LLMI_EXPORT int llmi_gemm_skinny(const void* x, long ldx, const void* w, long ld
                                  float* emit_ss, const float* in_ss, int in_tiles, float in_eps, int* error_flag,
                                  cudaStream_t stream) {
   if (n_tok <= 0 || n_tok > 64 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
-  if (mode < 0 || mode > OUT_RELU2_REQUEST) return LLMI_ERR_UNSUPPORTED;
-  const int act = mode == OUT_GEGLU_REQUEST ? 1 : (mode == OUT_RELU2_REQUEST ? ACT_STORE_RELU2 : 0);
+  if (mode < 0 || mode > OUT_GELU_REQUEST) return LLMI_ERR_UNSUPPORTED;
+  const int act = mode == OUT_GEGLU_REQUEST ? 1 : store_act_of(mode);
   if (mode == OUT_GEGLU_REQUEST) mode = SK_SWIGLU;
-  if (mode == OUT_RELU2_REQUEST) mode = SK_STORE;
+  if (mode == OUT_RELU2_REQUEST || mode == OUT_GELU_REQUEST) mode = SK_STORE;
   if (mode == SK_SWIGLU && ((m_out & 1) || bias)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
   if (k % 64) return LLMI_ERR_UNSUPPORTED;   // the 3-D view of the matrices needs whole 64-wide k slices

@@ -1097,10 +1097,10 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
                              int n_tok, int m_out, int k, int mode, float* workspace, long workspace_bytes,
                              int* tickets, int n_tickets, int* error_flag, cudaStream_t stream) {
   if (n_tok <= 0 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
-  if (mode < 0 || mode > OUT_RELU2_REQUEST) return LLMI_ERR_UNSUPPORTED;
-  const int act = mode == OUT_GEGLU_REQUEST ? 1 : (mode == OUT_RELU2_REQUEST ? ACT_STORE_RELU2 : 0);
+  if (mode < 0 || mode > OUT_GELU_REQUEST) return LLMI_ERR_UNSUPPORTED;
+  const int act = mode == OUT_GEGLU_REQUEST ? 1 : store_act_of(mode);
   if (mode == OUT_GEGLU_REQUEST) mode = OUT_SWIGLU;
-  if (mode == OUT_RELU2_REQUEST) mode = OUT_STORE;
+  if (mode == OUT_RELU2_REQUEST || mode == OUT_GELU_REQUEST) mode = OUT_STORE;
   if (mode == OUT_SWIGLU && ((m_out & 1) || bias)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
   const int bn = tc_bn(n_tok, m_out);

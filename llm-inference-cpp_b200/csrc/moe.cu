@@ -4,7 +4,12 @@
 //   llmi_moe_route    per token: the `top` largest of E fp32 logits (ties: the lower index), their softmax (fp32);
 //                     or (`mode` 1) scores s = logistic(logit), the `top` largest scores weighted by s / (sum of the
 //                     chosen s + 1e-20), optionally among the experts of the best `keep` of `n_groups` equal runs of
-//                     neighbouring experts only, a run's score being the sum of its two largest scores
+//                     neighbouring experts only, a run's score being the sum of its two largest scores;
+//                     or (`mode` 2) scores s = softmax over ALL E logits, the choice by s + correction (a learned
+//                     number per expert), the weights s * scale without a division by their sum.  In this mode the last
+//                     `n_identity` of the E router outputs stand for experts that hand their input on: such a choice
+//                     is written as index -1 (the product kernels skip it) and the token's summed weight of them to
+//                     `id_wt`, for llmi_moe_identity_add
 //   llmi_moe_up       per (token, choice): a = act(Wg_e h) * (Wu_e h), or a = act(Wu_e h) for experts
 //                     without a gate matrix                                                  [T, top, F] fp32
 //   llmi_moe_down     per token: y = sum over its choices, in the order of the choice, of weight * (Wd_e a)   [T, W] fp32
@@ -32,24 +37,47 @@ __device__ __forceinline__ void warp_best(float& best, int& best_e) {
 }
 
 // One warp per token.  MODE 0: softmax over the chosen logits.  MODE 1: logistic scores, normalised over the chosen.
+// MODE 2: softmax over all logits, chosen by score + correction, weighted by score * scale.
 template <int MODE>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, long ld, int E, int top, int n_groups, int keep,
-                 const int32_t* __restrict__ tok_seq, int32_t* __restrict__ idx, float* __restrict__ wt, int n_tokens) {
+                 const int32_t* __restrict__ tok_seq, int32_t* __restrict__ idx, float* __restrict__ wt, int n_tokens,
+                 const float* __restrict__ correction, float scale, int n_identity, float* __restrict__ id_wt) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (t >= n_tokens) return;
   if (tok_seq[t] < 0) {
     for (int j = lane; j < top; j += 32) { idx[(size_t)t * top + j] = -1; wt[(size_t)t * top + j] = 0.f; }
+    if (MODE == 2 && id_wt && lane == 0) id_wt[t] = 0.f;
     return;
   }
   float v[MOE_MAX_PER_LANE];
+  float s_all[MOE_MAX_PER_LANE];      // MODE 2: the scores themselves (v holds score + correction)
 #pragma unroll
   for (int i = 0; i < MOE_MAX_PER_LANE; ++i) {
     const int e = lane + 32 * i;
     v[i] = e < E ? logits[(size_t)t * ld + e] : -INFINITY;
     if (MODE == 1 && e < E) v[i] = 1.0f / (1.0f + expf(-v[i]));
+  }
+  if (MODE == 2) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MOE_MAX_PER_LANE; ++i) mx = fmaxf(mx, v[i]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < MOE_MAX_PER_LANE; ++i) {
+      s_all[i] = lane + 32 * i < E ? expf(v[i] - mx) : 0.f;
+      sum += s_all[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < MOE_MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      s_all[i] = s_all[i] / sum;
+      if (e < E) v[i] = s_all[i] + (correction ? correction[e] : 0.f);
+    }
   }
   if (n_groups > 1 && keep < n_groups) {
     // lane g keeps the score of run g (n_groups <= 32): the sum of its two largest scores
@@ -86,6 +114,7 @@ moe_route_kernel(const float* __restrict__ logits, long ld, int E, int top, int 
     }
   }
   float first = 0.f, denom = 0.f, mine = 0.f;      // lane j keeps choice j's weight before the division (top <= 32)
+  float id_total = 0.f;
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
@@ -96,22 +125,44 @@ moe_route_kernel(const float* __restrict__ logits, long ld, int E, int top, int 
     }
     warp_best(best, best_e);
     if (j == 0) first = best;                        // the largest logit: the softmax's shift
-    const float ex = MODE == 1 ? best : expf(best - first);
+    float ex = MODE == 1 ? best : expf(best - first);
+    if (MODE == 2) {                                 // the chosen expert's own score, from the lane that holds it
+      float mine_s = 0.f;
+#pragma unroll
+      for (int i = 0; i < MOE_MAX_PER_LANE; ++i)
+        if (lane + 32 * i == best_e) mine_s = s_all[i];
+      ex = warp_sum(mine_s) * scale;
+      if (best_e >= E - n_identity) {                // an expert that hands its input on
+        id_total += ex;
+        best_e = -1 - best_e;                        // (marked; written as -1 below)
+      }
+    }
     denom += ex;
     if (lane == j) mine = ex;
-    if (lane == 0) idx[(size_t)t * top + j] = best_e;
+    const int chosen = best_e < 0 ? -1 - best_e : best_e;
+    if (lane == 0) idx[(size_t)t * top + j] = best_e < 0 ? -1 : best_e;
+    best_e = chosen;
 #pragma unroll
     for (int i = 0; i < MOE_MAX_PER_LANE; ++i)
       if (lane + 32 * i == best_e) v[i] = -INFINITY;   // taken
   }
-  if (lane < top) wt[(size_t)t * top + lane] = MODE == 1 ? mine / (denom + 1e-20f) : mine / denom;
+  if (lane < top) wt[(size_t)t * top + lane] = MODE == 2 ? mine : MODE == 1 ? mine / (denom + 1e-20f) : mine / denom;
+  if (MODE == 2 && id_wt && lane == 0) id_wt[t] = id_total;
 }
 
-template <int ACT> __device__ __forceinline__ float moe_act(float g) {
-  if (ACT == 0) return g / (1.0f + expf(-g));
-  if (ACT == 2) { g = fmaxf(g, 0.f); return g * g; }
-  return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+// y[t, :] += id_wt[t] * h[t, :] — what the experts that hand their input on add for a token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_identity_add_kernel(const T* __restrict__ h, long ldh, const float* __restrict__ id_wt, float* __restrict__ y, long ldy, int W) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float w = id_wt[t];
+  if (w == 0.f) return;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) y[(size_t)t * ldy + c] = fmaf(w, to_f32(h[(size_t)t * ldh + c]), y[(size_t)t * ldy + c]);
 }
+
+template <int ACT> __device__ __forceinline__ float moe_act(float g) { return expert_act(g, ACT); }
 
 // A warp's dot product of a shared-memory fp32 vector with one weight row, 16 bytes per lane and load.
 template <typename T> struct Vec16;
@@ -206,16 +257,35 @@ using namespace llmi;
 // mode 0: softmax over the chosen logits; mode 1: logistic scores normalised over the chosen.  n_groups <= 1 or
 // keep >= n_groups: every expert can be chosen.
 LLMI_EXPORT int llmi_moe_route(const float* logits, long ld, int E, int top, int mode, int n_groups, int keep,
-                               const int32_t* tok_seq, int32_t* idx, float* wt, int n_tokens, cudaStream_t stream) {
+                               const int32_t* tok_seq, int32_t* idx, float* wt, int n_tokens, const float* correction,
+                               float scale, int n_identity, float* id_wt, cudaStream_t stream) {
   if (n_tokens <= 0 || E <= 0 || top <= 0 || top > E || top > 32 || E > 32 * MOE_MAX_PER_LANE) return LLMI_ERR_BAD_SIZE;
   if (n_groups > 1 && (n_groups > 32 || E % n_groups != 0 || keep < 1 || keep * (E / n_groups) < top)) return LLMI_ERR_BAD_SIZE;
+  if (n_identity < 0 || n_identity > E || (n_identity > 0 && (mode != 2 || !id_wt))) return LLMI_ERR_BAD_SIZE;
   if (mode == 0)
     return launch_pdl(PDL_SMALL, moe_route_kernel<0>, (n_tokens + 3) / 4, 128, 0, stream, logits, ld, E, top, n_groups, keep, tok_seq,
-                      idx, wt, n_tokens);
+                      idx, wt, n_tokens, correction, scale, n_identity, id_wt);
   if (mode == 1)
     return launch_pdl(PDL_SMALL, moe_route_kernel<1>, (n_tokens + 3) / 4, 128, 0, stream, logits, ld, E, top, n_groups, keep, tok_seq,
-                      idx, wt, n_tokens);
+                      idx, wt, n_tokens, correction, scale, n_identity, id_wt);
+  if (mode == 2) {
+    if (n_groups > 1) return LLMI_ERR_UNSUPPORTED;
+    return launch_pdl(PDL_SMALL, moe_route_kernel<2>, (n_tokens + 3) / 4, 128, 0, stream, logits, ld, E, top, n_groups, keep, tok_seq,
+                      idx, wt, n_tokens, correction, scale, n_identity, id_wt);
+  }
   return LLMI_ERR_UNSUPPORTED;
+}
+
+// y [T, ldy] fp32 += id_wt[t] * h[t] (h [T, ldh] in `dtype`).
+LLMI_EXPORT int llmi_moe_identity_add(int dtype, const void* h, long ldh, const float* id_wt, float* y, long ldy, int W,
+                                      int n_tokens, cudaStream_t stream) {
+  if (n_tokens <= 0 || W <= 0) return LLMI_ERR_BAD_SIZE;
+  if (dtype == LLMI_DTYPE_F32)
+    return launch_pdl(PDL_SMALL, moe_identity_add_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)h, ldh, id_wt, y, ldy, W);
+  if (dtype == LLMI_DTYPE_BF16)
+    return launch_pdl(PDL_SMALL, moe_identity_add_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, (const __nv_bfloat16*)h,
+                      ldh, id_wt, y, ldy, W);
+  return LLMI_ERR_BAD_DTYPE;
 }
 
 template <typename T, int ACT, bool VEC>
@@ -249,15 +319,18 @@ static int launch_moe_down(const float* a, const void* wd, int W, int F, int top
 LLMI_EXPORT int llmi_moe_up(int dtype, const void* h, long ldh, const void* wg, const void* wu, int W, int F, int top,
                             const int32_t* idx, float* a, int act, int n_tokens, cudaStream_t stream) {
   if (n_tokens <= 0 || W <= 0 || F <= 0 || top <= 0 || (size_t)W * 4 > 160 * 1024 || (F + 7) / 8 > 65535) return LLMI_ERR_BAD_SIZE;
-  if (act < 0 || act > 2) return LLMI_ERR_UNSUPPORTED;
+  if (act < 0 || act > 3) return LLMI_ERR_UNSUPPORTED;
   const int esz = dtype == LLMI_DTYPE_F32 ? 4 : 2;
   const bool vec = ((size_t)W * esz) % 16 == 0 && !((uintptr_t)wg & 15) && !((uintptr_t)wu & 15);
 #define LLMI_UP(T, ACT) \
   return vec ? launch_moe_up<T, ACT, true>(h, ldh, wg, wu, W, F, top, idx, a, n_tokens, stream) \
              : launch_moe_up<T, ACT, false>(h, ldh, wg, wu, W, F, top, idx, a, n_tokens, stream)
-  if (dtype == LLMI_DTYPE_F32) { if (act == 0) LLMI_UP(float, 0); else if (act == 1) LLMI_UP(float, 1); else LLMI_UP(float, 2); }
+  if (dtype == LLMI_DTYPE_F32) {
+    if (act == 0) LLMI_UP(float, 0); else if (act == 1) LLMI_UP(float, 1); else if (act == 2) LLMI_UP(float, 2); else LLMI_UP(float, 3);
+  }
   if (dtype == LLMI_DTYPE_BF16) {
-    if (act == 0) LLMI_UP(__nv_bfloat16, 0); else if (act == 1) LLMI_UP(__nv_bfloat16, 1); else LLMI_UP(__nv_bfloat16, 2);
+    if (act == 0) LLMI_UP(__nv_bfloat16, 0); else if (act == 1) LLMI_UP(__nv_bfloat16, 1);
+    else if (act == 2) LLMI_UP(__nv_bfloat16, 2); else LLMI_UP(__nv_bfloat16, 3);
   }
 #undef LLMI_UP
   return LLMI_ERR_BAD_DTYPE;

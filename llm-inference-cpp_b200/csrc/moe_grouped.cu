@@ -193,9 +193,7 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ A, long lda, const int32_t*
           if (c + 1 < N) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);
           else dst[0] = __float2bfloat16_rn(v0);
         } else if (MODE == 3) {
-          const float r0 = fmaxf(v0, 0.f), r1 = fmaxf(v1, 0.f);
-          const float a0 = ACT == 2 ? r0 * r0 : ACT == 0 ? v0 / (1.0f + expf(-v0)) : 0.5f * v0 * (1.0f + tanhf(0.7978845608028654f * (v0 + 0.044715f * v0 * v0 * v0)));
-          const float a1 = ACT == 2 ? r1 * r1 : ACT == 0 ? v1 / (1.0f + expf(-v1)) : 0.5f * v1 * (1.0f + tanhf(0.7978845608028654f * (v1 + 0.044715f * v1 * v1 * v1)));
+          const float a0 = expert_act(v0, ACT), a1 = expert_act(v1, ACT);
           __nv_bfloat16* dst = (__nv_bfloat16*)out + (size_t)(row0 + r) * ldo + c;
           if (c + 1 < N) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a0, a1);
           else dst[0] = __float2bfloat16_rn(a0);
@@ -257,7 +255,7 @@ struct GtParams {
   int N, K;                      // an expert's weight [N, K]
   void* out;                     // [items, N], row pitch ldo: bf16 act(v) (mode 0) or fp32 v (mode 1)
   long ldo;
-  int mode, act;                 // act 0: silu, 1: tanh GELU, 2: relu squared
+  int mode, act;                 // act 0: silu, 1: tanh GELU, 2: relu squared, 3: exact GELU
   const int32_t *offsets, *tile_expert, *tile_row0, *n_tiles;
   int* error_flag;
 };
@@ -393,11 +391,7 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             if (p.mode == 1) {
               ((float*)p.out)[idx] = x;
             } else {
-              const float r = fmaxf(x, 0.f);
-              const float a = p.act == 2 ? r * r
-                              : p.act == 0 ? x / (1.0f + expf(-x))
-                                           : 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
-              ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(a);
+              ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(expert_act(x, p.act));
             }
           }
         }
@@ -455,7 +449,7 @@ LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const 
   if ((W % 8) || (F % 8) || (ldh % 8) || ((uintptr_t)h & 15) || ((uintptr_t)wg & 15) || ((uintptr_t)wu & 15) || ((uintptr_t)wd & 15) ||
       ((uintptr_t)a_sorted & 15))
     return LLMI_ERR_ALIGN;
-  if (act < 0 || act > 2 || (act == 2 && wg)) return LLMI_ERR_UNSUPPORTED;
+  if (act < 0 || act > 3 || (act >= 2 && wg)) return LLMI_ERR_UNSUPPORTED;
   const int n_items = n_tokens * top;
   if (scratch_ints < llmi_moe_group_ints(n_items, E)) return LLMI_ERR_BAD_SIZE;
   const int max_tiles = (n_items + GB_M - 1) / GB_M + E;
@@ -518,6 +512,7 @@ LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const 
     cudaFuncSetAttribute(moe_grouped_kernel<3, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
     cudaFuncSetAttribute(moe_grouped_kernel<3, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
     cudaFuncSetAttribute(moe_grouped_kernel<3, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
+    cudaFuncSetAttribute(moe_grouped_kernel<3, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
     configured.here() = true;
   }
   if (!wg) {
@@ -525,7 +520,7 @@ LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const 
     rc = launch_pdl(PDL_GEMM, moe_grouped_kernel<3, ACT>, grid_up, dim3(128), smem_down, stream, hb, ldh, (const int32_t*)sorted_items, \
                     top, u, u, F, W, (const int32_t*)offsets, (const int32_t*)tile_expert, (const int32_t*)tile_row0,                 \
                     (const int32_t*)n_tiles, a_sorted, (long)F, 0, 0L, 0L)
-    if (act == 0) LLMI_UNGATED(0); else if (act == 1) LLMI_UNGATED(1); else LLMI_UNGATED(2);
+    if (act == 0) LLMI_UNGATED(0); else if (act == 1) LLMI_UNGATED(1); else if (act == 2) LLMI_UNGATED(2); else LLMI_UNGATED(3);
 #undef LLMI_UNGATED
   } else if (act == 0)
     rc = launch_pdl(PDL_GEMM, moe_grouped_kernel<0, 0>, grid_up, dim3(128), smem_up, stream, hb, ldh, (const int32_t*)sorted_items, top,

@@ -166,14 +166,19 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
   }
 }
 
-// out = act(x), elementwise; act 0: relu(x)^2.
+// out = act(x), elementwise; act 0: relu(x)^2; 1: the exact GELU 0.5 x (1 + erf(x / sqrt(2))); 2: silu.
+__device__ __forceinline__ float plain_act(float v, int act) {
+  if (act == 1) return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
+  if (act == 2) return v / (1.0f + expf(-v));
+  v = fmaxf(v, 0.f);
+  return v * v;
+}
 template <typename T>
 __global__ void activate_kernel(const T* __restrict__ x, T* __restrict__ out, int act, size_t total) {
   pdl_launch_dependents();
   pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const float v = fmaxf(to_f32(x[i]), 0.f);
-    out[i] = from_f32<T>(v * v);
+    out[i] = from_f32<T>(plain_act(to_f32(x[i]), act));
   }
 }
 
@@ -187,9 +192,7 @@ __global__ void activate_vec8_kernel(const uint4* __restrict__ x, uint4* __restr
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       float2 f = __bfloat1622float2(p[e]);
-      f.x = fmaxf(f.x, 0.f);
-      f.y = fmaxf(f.y, 0.f);
-      p[e] = __floats2bfloat162_rn(f.x * f.x, f.y * f.y);
+      p[e] = __floats2bfloat162_rn(plain_act(f.x, act), plain_act(f.y, act));
     }
     out[i] = raw;
   }
@@ -293,7 +296,7 @@ LLMI_EXPORT int llmi_swiglu(int dtype, const void* gate_up, void* out, int n_row
 
 LLMI_EXPORT int llmi_activate(int dtype, const void* x, void* out, long total, int act, cudaStream_t stream) {
   if (total <= 0) return LLMI_ERR_BAD_SIZE;
-  if (act != 0) return LLMI_ERR_UNSUPPORTED;
+  if (act < 0 || act > 2) return LLMI_ERR_UNSUPPORTED;
   const int threads = 256;
   const size_t most = (size_t)sm_count() * 16;       // a grid-stride loop takes the rest
   const size_t want = ((size_t)total + threads - 1) / threads;

@@ -19,7 +19,7 @@ __global__ void __launch_bounds__(128)
 conv_add_kernel(const T* __restrict__ h, long ldh, const float* __restrict__ w, const float* __restrict__ carry_all,
                 long carry_stride, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos,
                 const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_slot, T* __restrict__ y, long ldy,
-                int C, int K) {
+                int C, int K, int add_input) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -34,7 +34,7 @@ conv_add_kernel(const T* __restrict__ h, long ldh, const float* __restrict__ w, 
   const int pos = tok_pos[t], r0 = seq_q_start[seq];
   const int p0 = pos - (t - r0);                              // position of this sequence's first row of the step
   const float* carry = carry_all + (size_t)(slot < 0 ? 0 : slot) * carry_stride;
-  const float own = to_f32(h[(size_t)t * ldh + c]);
+  const float own = add_input ? to_f32(h[(size_t)t * ldh + c]) : 0.f;
   float acc = 0.f;
   for (int j = 0; j < K; ++j) {                               // oldest tap first
     const int p = pos - (K - 1) + j;
@@ -197,24 +197,25 @@ LLMI_EXPORT int llmi_norm_conv_token(int dtype, const float* x, const float* nor
   return LLMI_ERR_BAD_DTYPE;
 }
 
-// y = h + conv(h); h, y [T, C] in the type `dtype`; w fp32 [K, C] (tap-major); carry fp32 [slots, carry_stride >= (K-1)*C].
+// y = h + conv(h), or conv(h) alone without `add_input`; h, y [T, C] in the type `dtype`; w fp32 [K, C] (tap-major); carry fp32 [slots, carry_stride >= (K-1)*C].
 LLMI_EXPORT int llmi_conv_add(int dtype, const void* h, long ldh, const float* w, const float* carry, long carry_stride,
                               const int32_t* tok_seq, const int32_t* tok_pos, const int32_t* seq_q_start,
-                              const int32_t* seq_slot, void* y, long ldy, int n_tokens, int C, int K, cudaStream_t stream) {
+                              const int32_t* seq_slot, void* y, long ldy, int n_tokens, int C, int K, int add_input,
+                              cudaStream_t stream) {
   if (n_tokens <= 0 || C <= 0 || (C + 127) / 128 > 65535 || K < 1 || K > CONV_MAX_TAPS) return LLMI_ERR_BAD_SIZE;
   const dim3 grid(n_tokens, (C + 127) / 128);
   if (dtype == LLMI_DTYPE_F32)
     return launch_pdl(PDL_SMALL, conv_add_kernel<float>, grid, dim3(128), 0, stream, (const float*)h, ldh, w, carry, carry_stride,
-                      tok_seq, tok_pos, seq_q_start, seq_slot, (float*)y, ldy, C, K);
+                      tok_seq, tok_pos, seq_q_start, seq_slot, (float*)y, ldy, C, K, add_input);
   if (dtype == LLMI_DTYPE_BF16) {
-    if (C % 8 == 0 && ldh % 8 == 0 && ldy % 8 == 0 && !((uintptr_t)h & 15) && !((uintptr_t)y & 15) && !((uintptr_t)w & 15)) {
+    if (add_input && C % 8 == 0 && ldh % 8 == 0 && ldy % 8 == 0 && !((uintptr_t)h & 15) && !((uintptr_t)y & 15) && !((uintptr_t)w & 15)) {
       const int threads = C / 8 >= 128 ? 128 : ((C / 8 + 31) / 32) * 32;
       return launch_pdl(PDL_SMALL, conv_add_vec8_kernel, dim3(n_tokens, (C / 8 + threads - 1) / threads), dim3(threads), 0, stream,
                         (const __nv_bfloat16*)h, ldh, w, carry, carry_stride, tok_seq, tok_pos, seq_q_start, seq_slot,
                         (__nv_bfloat16*)y, ldy, C, K);
     }
     return launch_pdl(PDL_SMALL, conv_add_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)h, ldh, w, carry,
-                      carry_stride, tok_seq, tok_pos, seq_q_start, seq_slot, (__nv_bfloat16*)y, ldy, C, K);
+                      carry_stride, tok_seq, tok_pos, seq_q_start, seq_slot, (__nv_bfloat16*)y, ldy, C, K, add_input);
   }
   return LLMI_ERR_BAD_DTYPE;
 }

@@ -1,2 +1,2 @@
 """Architectures this library knows; importing the package registers them."""
-from . import fusazen, garodra, gemosun, llama  # noqa: F401
+from . import fusazen, garodra, gemosun, llama, renitar  # noqa: F401

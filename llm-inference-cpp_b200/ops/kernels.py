@@ -22,8 +22,9 @@ OUT_ADD_F32 = 2      # y (fp32) += x·Wᵀ
 OUT_SWIGLU = 3       # y (compute type) = silu(gate)·up, W's rows alternating gate and up rows (tensor-core kernel only)
 OUT_GEGLU = 4        # the same with the tanh form of GELU as the gate's activation
 OUT_RELU2 = 5        # y (compute type) = relu(x·Wᵀ + bias)², the activation finished in the product's epilogue
+OUT_GELU = 6         # y (compute type) = gelu(x·Wᵀ + bias), the exact form v·Phi(v), finished in the product's epilogue
 _GATED = (OUT_SWIGLU, OUT_GEGLU)
-_STORES = (OUT_STORE, OUT_RELU2)      # the modes whose output has the compute type and the weight's row count
+_STORES = (OUT_STORE, OUT_RELU2, OUT_GELU)      # the modes whose output has the compute type and the weight's row count
 
 _ERRORS = {
     -1: "unsupported element type",
@@ -160,7 +161,9 @@ def lib():
                      "llmi_moe_down", "llmi_moe_grouped", "llmi_linear_heads_mma", "llmi_attention_latent_mma", "llmi_attention_latent_mma_supported",
                      "llmi_conv_add", "llmi_conv_carry", "llmi_qkv_prepare", "llmi_attention_flex", "llmi_diff_combine",
                      "llmi_gdelta_prepare", "llmi_dplr_recurrence", "llmi_activate", "llmi_attention_maps_mma", "llmi_attention_maps_mma_supported", "llmi_tanh_rows", "llmi_norm_conv_token",
-                     "llmi_layernorm", "llmi_depth_mix", "llmi_gate_rows", "llmi_pool_rows", "llmi_mix_layernorm"):
+                     "llmi_layernorm", "llmi_depth_mix", "llmi_gate_rows", "llmi_pool_rows", "llmi_mix_layernorm",
+                     "llmi_moe_identity_add", "llmi_channel_decay", "llmi_rows_activate", "llmi_decay_recurrence",
+                     "llmi_normed_pair", "llmi_stream_axpy_norm"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_delta_state_floats.restype = c_long
@@ -257,7 +260,7 @@ def gate_rows(a: torch.Tensor, z: torch.Tensor) -> None:
 
 ACT_SILU, ACT_GELU_TANH = 0, 1
 ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
-EXPERT_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}      # of the routed experts' kernels (relu2: the square of relu)
+EXPERT_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2, "gelu": 3}      # of the routed experts' kernels (relu2: the square of relu; gelu: the exact form)
 FUSED_GATE_MODES = {ACT_SILU: OUT_SWIGLU, ACT_GELU_TANH: OUT_GEGLU}     # activation -> the output mode of the products that gate in their epilogue
 
 
@@ -474,9 +477,9 @@ def linear(x, w, out, bias=None, mode: int = OUT_STORE, then_norm: DeferredNorm 
         if x.source is None:
             raise KernelError("a deferred norm that no product has filled")
         rmsnorm(x.source, x.weight, x.h, x.eps)
-    if mode == OUT_RELU2:                # the fp32 FMA product has no activation in its epilogue: two steps
+    if mode in _STORE_ACTIVATIONS:       # the fp32 FMA product has no activation in its epilogue: two steps
         linear_simt(xin, w, out, bias, OUT_STORE)
-        activate(out, out, ACT_RELU2)
+        activate(out, out, _STORE_ACTIVATIONS[mode])
         return False
     linear_simt(xin, w, out, bias, mode)
     return False
@@ -943,14 +946,16 @@ def qkv_prepare(proj: torch.Tensor, n_q_heads: int, n_k_heads: int, dk: int, n_v
 
 def attention_flex(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_pages, page_size: int, n_heads: int,
                    n_kv_heads: int, maps: int, dk: int, dv: int, scale: float, head_scale=None, window: int = 0,
-                   chunk: int = 0, pooled=None, gate=None) -> None:
+                   chunk: int = 0, pooled=None, gate=None, softcap: float = 0.0) -> None:
     """Causal attention of every token over its sequence's cache with ``maps`` score maps per head (query row
     [head][map][dk], key heads [kv head][map], one set of values [kv head][dv]); out [T, heads*maps*dv] in q's type or
     fp32.  ``head_scale`` fp32 [heads] multiplies the scores of a head; ``window`` and ``chunk`` limit the visible keys
     (a query at p sees max(p - window + 1, p // chunk * chunk) .. p).  ``pooled`` = (pool, k_pool, v_pool, pool_pages):
     beside its window a query sees row b of the pooled pages for every block b of ``pool`` positions that lies wholly
     before the window (b * pool + pool - 1 <= p - window), in the same softmax.  ``gate`` fp32 [T, >= heads] (row-strided):
-    head h's output is multiplied by logistic(gate[t, h])."""
+    head h's output is multiplied by logistic(gate[t, h]); a gate of exactly heads*dv columns (one map) has a number per
+    output entry instead.  ``softcap`` > 0: a score s becomes softcap * tanh(s / softcap) before the softmax."""
+    gate_per = _gate_per(gate, n_heads, maps, dv)
     _need_cuda(q, out, k_cache, v_cache, seq_pages, head_scale, gate)
     T = q.shape[0]
     pool, k_pool, v_pool, pool_pages = pooled if pooled is not None else (0, None, None, None)
@@ -970,7 +975,15 @@ def attention_flex(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, se
         _ptr(seq_pages), c_int(seq_pages.stride(0)), c_int(page_size), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(maps),
         c_int(dk), c_int(dv), c_float(scale), _ptr(head_scale), c_int(window), c_int(chunk), c_int(pool), _ptr(k_pool), _ptr(v_pool),
         _ptr(pool_pages), c_int(pool_pages.stride(0) if pool else 0), _ptr(gate), c_long(gate.stride(0) if gate is not None else 0),
-        _stream()))
+        c_int(gate_per), c_float(softcap), _stream()))
+
+
+def _gate_per(gate, n_heads: int, maps: int, dv: int) -> int:
+    """How an output gate is laid out: 1 — a number per (token, head); dv — a number per output entry (a gate of
+    exactly heads*dv columns, one map, where that is not also the head count)."""
+    if gate is None or maps != 1 or dv == 1 or gate.shape[1] != n_heads * dv:
+        return 1
+    return dv
 
 
 def pool_rows(k_cache, v_cache, seq_pages, k_pool, v_pool, pool_pages, page_size: int, pool: int, ctx) -> None:
@@ -991,11 +1004,12 @@ def pool_rows(k_cache, v_cache, seq_pages, k_pool, v_pool, pool_pages, page_size
 
 def attention_maps(q, out, k_cache, v_cache, ctx, seq_pages, page_size: int, n_heads: int, n_kv_heads: int, maps: int,
                    dk: int, dv: int, scale: float, head_scale=None, window: int = 0, chunk: int = 0, rt=None, pooled=None,
-                   gate=None) -> None:
+                   gate=None, softcap: float = 0.0) -> None:
     """The attention of a step in its general form (arguments as :func:`attention_flex`): bf16 sizes that the
     tensor-core kernel takes go there — prompts as blocks of 128 query rows, steps of single tokens cut over the
     positions (``rt`` lends the workspace of the cuts) —, everything else, and the 32-bit path, to the generic kernel."""
-    if (not ctx.decode and maps == 1 and chunk == 0 and head_scale is None and dk == dv and page_size == 64 and scale > 0
+    gate_per = _gate_per(gate, n_heads, maps, dv)
+    if (not ctx.decode and maps == 1 and chunk == 0 and head_scale is None and dk == dv and softcap == 0.0 and gate_per == 1 and page_size == 64 and scale > 0
             and q.dtype == out.dtype == k_cache.dtype == torch.bfloat16 and rt is not None and _MAPS_ATTENTION == "mma"
             and _PREFILL_ATTENTION == "tc" and not _FORCE_GENERIC_ATTENTION and attention_prefill_tc_supported(dk)
             and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
@@ -1045,10 +1059,10 @@ def attention_maps(q, out, k_cache, v_cache, ctx, seq_pages, page_size: int, n_h
             c_int(dv), c_float(scale), _ptr(head_scale), c_int(window), c_int(chunk), c_int(1 if prompt else 0),
             c_int(T // 128 + S), c_int(splits), c_int(pps), _ptr(ws), c_long(n_ws), c_int(pool), _ptr(k_pool), _ptr(v_pool),
             _ptr(pool_pages), c_int(pool_pages.stride(0) if pool else 0), _ptr(gate),
-            c_long(gate.stride(0) if gate is not None else 0), _stream()))
+            c_long(gate.stride(0) if gate is not None else 0), c_int(gate_per), c_float(softcap), _stream()))
         return
     attention_flex(q, out, k_cache, v_cache, ctx, seq_pages, page_size, n_heads, n_kv_heads, maps, dk, dv, scale, head_scale,
-                   window, chunk, pooled, gate)
+                   window, chunk, pooled, gate, softcap)
 
 
 _MAPS_ATTENTION = os.environ.get("LLMI_MAPS_ATTENTION", "mma")      # "generic": the fp32-arithmetic kernel for everything
@@ -1084,8 +1098,9 @@ def diff_combine(a: torch.Tensor, lam: float, eps: float, post: float, H: int, d
 # ---------------------------------------------------------------------------------------------
 # A short convolution over time with a carried state (csrc/short_conv.cu); plain activations
 
-def conv_add(h: torch.Tensor, w: torch.Tensor, carry: torch.Tensor, ctx, out: torch.Tensor, write_state: bool = True) -> None:
-    """out = h + conv(h): per channel a causal convolution over time with the taps ``w`` fp32 [K, C] (tap-major: the
+def conv_add(h: torch.Tensor, w: torch.Tensor, carry: torch.Tensor, ctx, out: torch.Tensor, write_state: bool = True,
+             add_input: bool = True) -> None:
+    """out = h + conv(h) (or conv(h) alone with ``add_input`` False; ``h`` may be a view of wider rows): per channel a causal convolution over time with the taps ``w`` fp32 [K, C] (tap-major: the
     channels of a tap lie side by side; the oldest tap first); the K-1 inputs ahead of a step's first row come from
     ``carry`` fp32 [slots, >= (K-1)*C], which is then brought up to date."""
     _need_cuda(h, w, carry, out)
@@ -1097,7 +1112,8 @@ def conv_add(h: torch.Tensor, w: torch.Tensor, carry: torch.Tensor, ctx, out: to
     assert out.data_ptr() != h.data_ptr()
     _check("conv_add", lib().llmi_conv_add(c_int(_dtype_code(h)), _ptr(h), c_long(h.stride(0)), _ptr(w), _ptr(carry),
                                            c_long(carry.stride(0)), _ptr(ctx.tok_seq), _ptr(ctx.tok_pos), _ptr(ctx.seq_q_start),
-                                           _ptr(ctx.seq_slot), _ptr(out), c_long(out.stride(0)), c_int(T), c_int(C), c_int(K), _stream()))
+                                           _ptr(ctx.seq_slot), _ptr(out), c_long(out.stride(0)), c_int(T), c_int(C), c_int(K),
+                                           c_int(1 if add_input else 0), _stream()))
     if write_state and K > 1:
         _check("conv_carry", lib().llmi_conv_carry(c_int(_dtype_code(h)), _ptr(h), c_long(h.stride(0)), _ptr(carry),
                                                    c_long(carry.stride(0)), _ptr(ctx.seq_q_start), _ptr(ctx.seq_kv_len),
@@ -1121,13 +1137,14 @@ def norm_conv_token(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w: torch.
         c_int(1 if write_state else 0), _stream()))
 
 
-ACT_RELU2 = 0
-PLAIN_ACTIVATIONS = {"relu2": ACT_RELU2}
-PLAIN_ACTIVATION_MODES = {ACT_RELU2: OUT_RELU2}      # activation -> the output mode of the products that finish it in their epilogue
+ACT_RELU2, ACT_GELU = 0, 1
+PLAIN_ACTIVATIONS = {"relu2": ACT_RELU2, "gelu": ACT_GELU}
+PLAIN_ACTIVATION_MODES = {ACT_RELU2: OUT_RELU2, ACT_GELU: OUT_GELU}      # activation -> the output mode of the products that finish it in their epilogue
+_STORE_ACTIVATIONS = {mode: act for act, mode in PLAIN_ACTIVATION_MODES.items()}
 
 
 def activate(x: torch.Tensor, out: torch.Tensor, act: int = ACT_RELU2) -> None:
-    """out = act(x), elementwise (in place if out is x); act: the square of relu."""
+    """out = act(x), elementwise (in place if out is x); act: the square of relu, or the exact GELU."""
     _need_cuda(x, out)
     assert x.is_contiguous() and out.is_contiguous() and x.shape == out.shape and x.dtype == out.dtype
     _check("activate", lib().llmi_activate(c_int(_dtype_code(x)), _ptr(x), _ptr(out), c_long(x.numel()), c_int(act), _stream()))
@@ -1381,25 +1398,43 @@ def dplr_recurrence(proj: torch.Tensor, prep: torch.Tensor, H: int, D: int, Dv: 
 # Routed experts
 
 ROUTE_SOFTMAX_CHOSEN, ROUTE_LOGISTIC_NORMALISED = 0, 1
-ROUTE_MODES = {"softmax_chosen": ROUTE_SOFTMAX_CHOSEN, "logistic_normalised": ROUTE_LOGISTIC_NORMALISED}
+ROUTE_SOFTMAX_ALL = 2      # scores: the softmax over ALL logits; chosen by score + correction; weights: score * scale, not normalised
+ROUTE_MODES = {"softmax_chosen": ROUTE_SOFTMAX_CHOSEN, "logistic_normalised": ROUTE_LOGISTIC_NORMALISED,
+               "softmax_all": ROUTE_SOFTMAX_ALL}
 
 
 def moe_route(logits: torch.Tensor, top: int, ctx, idx: torch.Tensor, wt: torch.Tensor, mode: int = ROUTE_SOFTMAX_CHOSEN,
-              n_groups: int = 0, keep: int = 0, experts: int | None = None) -> None:
+              n_groups: int = 0, keep: int = 0, experts: int | None = None, correction: torch.Tensor | None = None,
+              scale: float = 1.0, identity: int = 0, id_wt: torch.Tensor | None = None) -> None:
     """The ``top`` largest of each row's fp32 logits (ties: the lower index) into ``idx`` int32 [T, top], and the
     softmax over them into ``wt`` fp32 [T, top]; a token row of no sequence gets index -1.  ``mode``
     ROUTE_LOGISTIC_NORMALISED: the scores are logistic(logit) and the weights the chosen scores over their sum (+ 1e-20).
     ``n_groups`` > 1 with ``keep`` < n_groups: only experts of the ``keep`` best of ``n_groups`` equal runs of neighbours
     can be chosen (a run's score: the sum of its two largest scores).  ``experts``: the first columns of ``logits`` that
-    are experts (default: all)."""
-    _need_cuda(logits, idx, wt)
+    are experts (default: all).  ``mode`` ROUTE_SOFTMAX_ALL: the scores are the softmax over all ``experts`` logits, the
+    choice goes by score + ``correction`` (fp32 [experts], optional), the weights are the chosen scores times ``scale``;
+    the last ``identity`` of the experts hand their input on: such a choice gets index -1 and the token's summed weight
+    of them goes to ``id_wt`` fp32 [T] (see :func:`moe_identity_add`)."""
+    _need_cuda(logits, idx, wt, correction, id_wt)
+    assert correction is None or (correction.dtype == torch.float32 and correction.is_contiguous())
+    assert id_wt is None or (id_wt.dtype == torch.float32 and id_wt.is_contiguous() and id_wt.numel() >= logits.shape[0])
     T, E = logits.shape
     E = E if experts is None else int(experts)
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and idx.dtype == torch.int32 and wt.dtype == torch.float32
     assert idx.shape == (T, top) and wt.shape == (T, top) and idx.is_contiguous() and wt.is_contiguous()
     _check("moe_route", lib().llmi_moe_route(_ptr(logits), c_long(logits.stride(0)), c_int(E), c_int(top), c_int(mode),
                                              c_int(n_groups), c_int(keep), _ptr(ctx.tok_seq), _ptr(idx), _ptr(wt), c_int(T),
-                                             _stream()))
+                                             _ptr(correction), c_float(scale), c_int(identity), _ptr(id_wt), _stream()))
+
+
+def moe_identity_add(h: torch.Tensor, id_wt: torch.Tensor, y: torch.Tensor) -> None:
+    """y[t] += id_wt[t] * h[t]: what a token's chosen experts that hand their input on add.  h [T, W] in the compute type
+    (row-strided), id_wt fp32 [T], y fp32 [T, W] (row-strided)."""
+    _need_cuda(h, id_wt, y)
+    T, W = h.shape
+    assert h.stride(1) == 1 and y.stride(1) == 1 and y.shape == (T, W) and y.dtype == id_wt.dtype == torch.float32
+    _check("moe_identity_add", lib().llmi_moe_identity_add(c_int(_dtype_code(h)), _ptr(h), c_long(h.stride(0)), _ptr(id_wt), _ptr(y),
+                                                           c_long(y.stride(0)), c_int(W), c_int(T), _stream()))
 
 
 def moe_experts_streamed(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int, a: torch.Tensor, y: torch.Tensor,
@@ -1451,3 +1486,76 @@ def moe_experts_grouped(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int
         _ptr(h), c_long(h.stride(0)), _ptr(w_gate), _ptr(w_up), _ptr(w_down), c_int(W), c_int(F), c_int(E), c_int(top), _ptr(idx),
         _ptr(wt), c_int(act), _ptr(scratch), c_long(n_int), _ptr(a_sorted), _ptr(y_sorted), _ptr(y), c_long(y.stride(0)), c_int(T),
         c_int(1 if add else 0), _ptr(h_sorted), _ptr(tc_scratch(h.device).error), _stream()))
+
+
+# ---------------------------------------------------------------------------------------------
+# Linear attention with a decay (csrc/decay_recurrence.cu)
+
+def channel_decay(low: torch.Tensor, w2t: torch.Tensor, bias, tau: float, ctx, dec: torch.Tensor) -> None:
+    """dec[t, c] = logistic(bias[c] + sum_j w2t[j, c] * low[t, j]) ** (1 / tau), in fp32 (as exp(log_logistic(z) / tau)).
+    low fp32 [T, R] (a view of wider rows), w2t fp32 [R, N], bias fp32 [N] or None, dec fp32 [T, N]."""
+    _need_cuda(low, w2t, bias, dec)
+    T, R = low.shape
+    N = w2t.shape[1]
+    assert low.dtype == w2t.dtype == dec.dtype == torch.float32 and low.stride(1) == 1 and dec.stride(1) == 1
+    assert w2t.shape == (R, N) and w2t.is_contiguous() and dec.shape == (T, N) and (bias is None or (bias.dtype == torch.float32 and bias.numel() == N))
+    _check("channel_decay", lib().llmi_channel_decay(_ptr(low), c_long(low.stride(0)), c_int(R), _ptr(w2t), _ptr(bias), c_float(tau),
+                                                     c_int(N), _ptr(ctx.tok_seq), _ptr(dec), c_long(dec.stride(0)), c_int(T), _stream()))
+
+
+def rows_silu(x: torch.Tensor) -> None:
+    """x = silu(x) in place; x fp32 [T, n], a view of wider rows."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.stride(1) == 1
+    _check("rows_activate", lib().llmi_rows_activate(_ptr(x), c_long(x.stride(0)), c_int(x.shape[1]), c_int(x.shape[0]), c_int(0), _stream()))
+
+
+def decay_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, H: int, D: int, Dv: int, state: torch.Tensor, ctx,
+                     o_raw: torch.Tensor, dec: torch.Tensor | None = None, head_decay: torch.Tensor | None = None,
+                     q_scale: float = 1.0, write_state: bool = True) -> None:
+    """Per sequence and head, over the step's tokens:  S <- diag(w) S + k v^T,  o = q_scale * S^T q.  q, k (H*D entries) and
+    v (H*Dv) lie in the fp32 rows ``proj`` at the given column offsets; w is ``dec`` fp32 [T, H*D] (a factor per key channel
+    and token) or ``head_decay`` fp32 [H] (one constant factor per head).  ``state`` fp32 [slots, >= H*D*Dv] holds S column
+    by column and is continued; ``o_raw`` fp32 [T, H*Dv]."""
+    _need_cuda(proj, state, o_raw, dec, head_decay)
+    T = proj.shape[0]
+    assert proj.dtype == state.dtype == o_raw.dtype == torch.float32 and proj.stride(1) == 1 and o_raw.stride(1) == 1
+    assert state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= H * D * Dv and o_raw.shape == (T, H * Dv)
+    assert (dec is None) != (head_decay is None)
+    assert dec is None or (dec.dtype == torch.float32 and dec.shape == (T, H * D) and dec.stride(1) == 1)
+    assert head_decay is None or (head_decay.dtype == torch.float32 and head_decay.numel() == H and head_decay.is_contiguous())
+    assert max(q_off, k_off) + H * D <= proj.shape[1] and v_off + H * Dv <= proj.shape[1]
+    _check("decay_recurrence", lib().llmi_decay_recurrence(
+        _ptr(proj), c_long(proj.stride(0)), c_int(q_off), c_int(k_off), c_int(v_off), _ptr(dec),
+        c_long(dec.stride(0) if dec is not None else 0), _ptr(head_decay), c_float(q_scale), c_int(H), c_int(D), c_int(Dv),
+        _ptr(state), c_long(state.stride(0)), _ptr(ctx.seq_q_start), _ptr(ctx.seq_slot), _ptr(o_raw), c_long(o_raw.stride(0)),
+        c_int(ctx.n_seqs), c_int(1 if write_state else 0), _stream()))
+
+
+# ---------------------------------------------------------------------------------------------
+# Joining the branches of a layer (csrc/branch_parts.cu)
+
+def normed_pair(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor, eps: float, coeff: float, y: torch.Tensor,
+                add: bool = False) -> None:
+    """y (+)= coeff * (a / rms(a) * wa + b / rms(b) * wb) row by row, rms(v) = sqrt(mean(v^2) + eps); all fp32 [T, W]."""
+    _need_cuda(a, wa, b, wb, y)
+    T, W = a.shape
+    assert a.dtype == b.dtype == y.dtype == wa.dtype == wb.dtype == torch.float32 and b.shape == (T, W) and y.shape == (T, W)
+    assert a.stride(1) == 1 and b.stride(1) == 1 and y.stride(1) == 1 and wa.numel() == W and wb.numel() == W
+    _check("normed_pair", lib().llmi_normed_pair(_ptr(a), c_long(a.stride(0)), _ptr(wa), _ptr(b), c_long(b.stride(0)), _ptr(wb),
+                                                 c_float(eps), c_float(coeff), _ptr(y), c_long(y.stride(0)), c_int(W), c_int(T),
+                                                 c_int(1 if add else 0), _stream()))
+
+
+def stream_axpy_norm(x: torch.Tensor, y: torch.Tensor, m: float, norm_w: torch.Tensor | None = None, eps: float = 0.0,
+                     h: torch.Tensor | None = None) -> None:
+    """x += m * y (fp32 [T, W], contiguous).  With ``norm_w`` (fp32 [W]) and ``h`` [T, W] (compute type, contiguous): also
+    h = norm_w * x / rms(x) of the new x, in the same pass."""
+    _need_cuda(x, y, norm_w, h)
+    T, W = x.shape
+    assert x.dtype == y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape == (T, W)
+    assert (norm_w is None) == (h is None)
+    if h is not None:
+        assert norm_w.dtype == torch.float32 and norm_w.numel() == W and h.shape == (T, W) and h.is_contiguous()
+    _check("stream_axpy_norm", lib().llmi_stream_axpy_norm(_ptr(x), _ptr(y), c_float(m), c_int(T), c_int(W), _ptr(norm_w), c_float(eps),
+                                                           c_int(_dtype_code(h) if h is not None else 0), _ptr(h), _stream()))

@@ -345,3 +345,117 @@ class WindowPoolAttention(_MapsAttention):
         return self._project_out(out, x, store, then_norm)
 
     stores_output = True
+
+
+@part("mixer", "gated_attention")
+class GatedAttention(_MapsAttention):
+    """Softmax attention of grouped queries with optional pieces, each a parameter:
+
+    * ``bias``: the q, k, v and output projections have biases (the tensor's name + ``.b``);
+    * ``conv`` (taps; 0: none): a short causal convolution over time on every channel of q, k and v, right behind the
+      projection: y[t] = sum_j w[:, j] * u[t - taps + 1 + j], zeros before the sequence's start, no bias, the input itself
+      not added.  The last taps - 1 projected rows of a sequence are kept in the cache's state slab (fp32);
+    * ``qk_norm``: an RMS norm over the WHOLE q row and the whole k row (all heads at once, a plain weight per entry),
+      before the rotation;
+    * ``position``: a PartSpec of the position family whose rotation of pairs the preparation kernel applies to the first
+      entries of every q and k head;
+    * ``softcap`` (0: none): a score s becomes softcap * tanh(s / softcap) before the softmax;
+    * ``chunk`` / ``window``: the keys a query sees (see :class:`_MapsAttention`);
+    * ``gate``: every output entry is multiplied by logistic(W_g h) of its own, before the output projection.
+
+    params: ``width``, ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``eps`` (of the q and k norms), and the
+    above.  tensors: ``q`` [heads*dim, width], ``k`` [kv_heads*dim, width], ``v`` [kv_heads*vdim, width], ``o`` [width,
+    heads*vdim]; with ``bias`` ``q.b``, ``k.b``, ``v.b``, ``o.b``; with ``conv`` ``q.conv``, ``k.conv``, ``v.conv``
+    [channels, taps]; with ``qk_norm`` ``q.norm``, ``k.norm``; with ``gate`` ``g`` [heads*vdim, width]."""
+    stores_output = True
+    defers_norm = False
+
+    @classmethod
+    def declare(cls, spec):
+        p = spec.params
+        d = cls._declare_projections(p, 1)
+        H, G, D, Dv, W = p["heads"], p["kv_heads"], p["dim"], p["vdim"], p["width"]
+        if p.get("bias", False):
+            d.update({"q.b": TensorDecl((H * D,), "bias"), "k.b": TensorDecl((G * D,), "bias"),
+                      "v.b": TensorDecl((G * Dv,), "bias"), "o.b": TensorDecl((W,), "bias")})
+        if p.get("conv", 0):
+            K = p["conv"]
+            d.update({"q.conv": TensorDecl((H * D, K)), "k.conv": TensorDecl((G * D, K)), "v.conv": TensorDecl((G * Dv, K))})
+        if p.get("qk_norm", False):
+            d.update({"q.norm": TensorDecl((H * D,), "norm_scale"), "k.norm": TensorDecl((G * D,), "norm_scale")})
+        if p.get("gate", False):
+            d["g"] = TensorDecl((H * Dv, W))
+        if p.get("position") is not None:
+            d.update(nested_declare("position", p["position"]))
+        return d
+
+    def __init__(self, spec, tensors, rt, **_):
+        p = dict(spec.params)
+        p.setdefault("eps", 0.0)
+        self.rt = rt
+        self._sizes(p)
+        if self.shares_kv:
+            raise ValueError("gated_attention: has key and value projections of its own")
+        H, G, D, Dv = self.H, self.G, self.D, self.Dv
+        self.n_qkv = H * D + G * D + G * Dv
+        self.softcap = float(p.get("softcap", 0.0) or 0.0)
+        self.gated = bool(p.get("gate", False))
+        self.taps = int(p.get("conv", 0) or 0)
+        names = ["q", "k", "v"] + (["g"] if self.gated else [])
+        self.w_in = rt.to_compute(torch.cat([tensors[n] for n in names], dim=0))       # one product: [q | k | v | (gate)]
+        self.w_o = rt.to_compute(tensors["o"])
+        self.b_in = self.b_o = None
+        if p.get("bias", False):
+            parts = [tensors["q.b"].float(), tensors["k.b"].float(), tensors["v.b"].float()]
+            if self.gated:
+                parts.append(torch.zeros(H * Dv, dtype=torch.float32, device=parts[0].device))
+            self.b_in, self.b_o = rt.to_f32(torch.cat(parts)), rt.to_f32(tensors["o.b"])
+        self.conv_w = None
+        if self.taps:        # [taps, channels]: neighbouring channels side by side, the oldest tap first
+            self.conv_w = rt.to_f32(torch.cat([tensors[n + ".conv"] for n in ("q", "k", "v")], dim=0)).t().contiguous()
+        if p.get("qk_norm", False):
+            self.q_norm_w, self.k_norm_w = rt.to_f32(tensors["q.norm"]), rt.to_f32(tensors["k.norm"])
+        self.pairing, self.amplitude = 0, 1.0
+        if p.get("position") is not None:
+            self.position = nested_build("position", p["position"], tensors, rt)
+            self.inv_freq, self.rot_dims = self.position.inv_freq, int(self.position.rotary_dim)
+            self.pairing, self.amplitude = int(self.position.pairing), float(self.position.amplitude)
+            if self.rot_dims > D:
+                raise ValueError("gated_attention: the rotated part is larger than a head")
+
+    def more_cache_requests(self):
+        if self.taps <= 1:
+            return {}
+        from ..cache.storage import StateRequest
+        return {"conv": StateRequest(((self.taps - 1) * self.n_qkv,), torch.float32)}
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_o))
+
+    def forward(self, h, x, ctx, binding, store: bool = False, then_norm=None) -> bool:
+        T = h.shape[0]
+        rt, H, G, D, Dv = self.rt, self.H, self.G, self.D, self.Dv
+        proj = rt.scratch("attn_proj", (T, self.w_in.shape[0]), torch.float32)
+        kernels.linear(h, self.w_in, proj, self.b_in, kernels.OUT_STORE_F32)
+        qkv = proj
+        if self.taps:
+            qkv = rt.scratch("attn_conv", (T, self.n_qkv), torch.float32)
+            if self.taps > 1:
+                cb = binding.more["conv"]
+                carry = cb.group.data[cb.index]
+            else:
+                carry = rt.scratch("attn_conv_none", (1, 1), torch.float32)
+            kernels.conv_add(proj[:, :self.n_qkv], self.conv_w, carry, ctx, qkv, write_state=binding.writes, add_input=False)
+        g = binding.group
+        pages = ctx.pages_of(g)
+        k_cache, v_cache = g.k[binding.index], g.v[binding.index]
+        q = rt.scratch("attn_q", (T, H * D))
+        kernels.qkv_prepare(qkv, H, G, D, G, Dv, self.q_norm_w, self.k_norm_w, self.eps, self.inv_freq, self.rot_dims, ctx, pages,
+                            g.page_size, k_cache, v_cache, q, has_kv=True, write_kv=binding.writes, pairing=self.pairing,
+                            amplitude=self.amplitude)
+        out = rt.scratch("attn_out", (T, H * Dv))
+        kernels.attention_maps(q, out, k_cache, v_cache, ctx, pages, g.page_size, H, G, 1, D, Dv, self.scale, None,
+                               self.window, self.chunk, rt=rt, gate=proj[:, self.n_qkv:] if self.gated else None,
+                               softcap=self.softcap)
+        kernels.linear(out, self.w_o, x, self.b_o, kernels.OUT_STORE_F32 if store else kernels.OUT_ADD_F32)
+        return False

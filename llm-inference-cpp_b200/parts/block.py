@@ -105,6 +105,44 @@ class ParallelBlock:
         self.ffn.forward(h2, x, ctx)
 
 
+@part("block", "parallel_scaled")
+class ScaledParallelBlock:
+    """Both sublayers read ONE norm's output, and what they add is multiplied by a constant:
+    x += m * (mixer(norm(x)) + ffn(norm(x))).  The feed-forward may be absent.  The sublayers write their sum into an
+    fp32 buffer of its own (the mixer stores, the feed-forward adds: both must take ``store=``), and one pass joins it
+    to the stream; where the norm that reads x next offers ``after_scaled_add`` (the next block's first norm, handed in
+    as ``next_norm``), that norm is computed in the same pass and the next block takes its output as ``entry``.
+
+    Slots: ``mixer_norm``, ``mixer``, optional ``ffn``.  Parameter: ``residual_mult`` (m)."""
+
+    def __init__(self, mixer_norm, mixer, ffn=None, residual_mult: float = 1.0):
+        for p in (mixer, ffn):
+            if p is not None and not getattr(p, "stores_output", False):
+                raise ValueError(f"parallel_scaled: the part {getattr(p, 'kind', p)!r} cannot store its output (store=)")
+        self.mixer_norm, self.mixer, self.ffn = mixer_norm, mixer, ffn
+        self.m = float(residual_mult)
+        self.rt = mixer_norm.rt
+
+    @property
+    def takes_padding_rows(self) -> bool:
+        return True          # rows are treated alone
+
+    @property
+    def entry_norm(self):
+        return self.mixer_norm
+
+    def forward(self, x, ctx, binding, entry=None, next_norm=None):
+        h = entry if isinstance(entry, torch.Tensor) else self.mixer_norm.forward(x)
+        y = self.rt.scratch("branch_out", tuple(x.shape), torch.float32)
+        self.mixer.forward(h, y, ctx, binding, store=True)
+        if self.ffn is not None:
+            self.ffn.forward(h, y, ctx)
+        if hasattr(next_norm, "after_scaled_add"):
+            return next_norm.after_scaled_add(x, y, self.m)       # (this block's own h is read out by now)
+        kernels.stream_axpy_norm(x, y, self.m)
+        return None
+
+
 @part("block", "prepost")
 class PrePostNormBlock:
     """A norm ahead of AND behind each sublayer:  x += post1(mixer(pre1(x)));  x += post2(ffn(pre2(x))).

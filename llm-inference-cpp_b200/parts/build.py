@@ -7,7 +7,7 @@ the parts appear.
 """
 from __future__ import annotations
 
-from . import attention, block, conv, delta, depth, embedding, experts, feedforward, latent, loop, norm, position  # noqa: F401  (register the built-in parts)
+from . import attention, block, conv, decay, delta, depth, embedding, experts, feedforward, latent, loop, norm, position, sidebyside  # noqa: F401  (register the built-in parts)
 from .registry import TensorDecl, get_part
 from .spec import ModelSpec, PartSpec
 
@@ -66,9 +66,10 @@ def build_parts(spec: ModelSpec, tensors: dict, rt):
     for i, ls in enumerate(spec.layers):
         parts = {slot: _make(family, ps, tensors, rt) for slot, family, ps in ls.slots()}
         try:
-            block = get_part("block", ls.block)(**parts)
+            block = get_part("block", ls.block)(**parts, **ls.block_params)
         except TypeError as e:
-            raise ValueError(f"layer {i}: the arrangement {ls.block!r} does not take the slots {sorted(parts)}: {e}") from None
+            raise ValueError(f"layer {i}: the arrangement {ls.block!r} does not take the slots {sorted(parts)} "
+                             f"with the parameters {sorted(ls.block_params)}: {e}") from None
         layers.append(BuiltLayer(block, parts))
     final_norm = _make("norm", spec.final_norm, tensors, rt)
     head = _make("head", spec.head, tensors, rt, embedding=emb)

@@ -10,8 +10,9 @@ from .registry import TensorDecl, part
 
 @part("norm", "rms")
 class RMSNorm:
-    """params: ``width``, ``eps``, optional ``tensor`` (the weight's local name; default ``weight``).  tensors: the
-    weight [width] (kept in fp32)."""
+    """params: ``width``, ``eps``, optional ``tensor`` (the weight's local name; default ``weight``), optional
+    ``one_plus`` (the file stores the weight around zero: y = (1 + w) · x · rsqrt(mean(x²) + eps); the sum 1 + w is made
+    once at load, in fp32).  tensors: the weight [width] (kept in fp32)."""
     takes_padding_rows = True       # token rows of no sequence (a step padded to a shape) do no harm: rows are treated alone
 
     @classmethod
@@ -22,6 +23,8 @@ class RMSNorm:
         self.width = int(spec.params["width"])
         self.eps = float(spec.params["eps"])
         self.weight = rt.to_f32(tensors[spec.params.get("tensor", "weight")])
+        if spec.params.get("one_plus", False):
+            self.weight = (self.weight + 1.0).contiguous()
         self.rt = rt
 
     def forward(self, x, rows=None, scratch_name: str = "norm_out"):
@@ -29,6 +32,12 @@ class RMSNorm:
         n = x.shape[0] if rows is None else rows.shape[0]
         out = self.rt.scratch(scratch_name, (n, self.width))
         kernels.rmsnorm(x, self.weight, out, self.eps, rows)
+        return out
+
+    def after_scaled_add(self, x, y, m: float, scratch_name: str = "norm_out"):
+        """x += m * y, and this norm of the new x, in one pass over the rows; returns the norm's output."""
+        out = self.rt.scratch(scratch_name, (x.shape[0], self.width))
+        kernels.stream_axpy_norm(x, y, m, self.weight, self.eps, out)
         return out
 
     def deferred(self, n_tokens: int, name: str):

@@ -25,7 +25,8 @@ class LayerSpec:
     The four usual slots have fields of their own; any of them may be None (a layer without a
     feed-forward, say), and ``more`` adds slots by name — ``(slot, family, PartSpec)`` triples, for an
     arrangement with further norms or a second feed-forward.  The block class is built with one keyword
-    argument per filled slot.  The part in the slot ``mixer``, if any, is the one whose cache the layer keeps.
+    argument per filled slot, and one per entry of ``block_params`` (constants of the arrangement itself: a factor
+    on what the sublayers add, say).  The part in the slot ``mixer``, if any, is the one whose cache the layer keeps.
     """
     block: str                      # arrangement, e.g. "prenorm"
     mixer_norm: Optional[PartSpec] = None
@@ -33,6 +34,7 @@ class LayerSpec:
     ffn_norm: Optional[PartSpec] = None
     ffn: Optional[PartSpec] = None
     more: tuple = ()                # ((slot, family, PartSpec), ...)
+    block_params: dict = field(default_factory=dict)      # keyword arguments of the arrangement beside its parts
 
     def slots(self):
         """(slot, family, PartSpec) of every filled slot, in the order the tensors are declared."""
