@@ -2,9 +2,10 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --workload smollm2-360m|smollm2-135m [--workload-dtypes bfloat16,float32]
-    python bench.py --design garodra|fusazen|gemosun [--design-sizes 2048,1024]          (its own JSON line: that design's prefill and
-                                                                                  decode beside the Llama decoder at equal size;
-                                                                                  garodra also has the size 2048-looped)
+    python bench.py --design garodra|fusazen|gemosun|renitar [--design-sizes 2048,1024]          (its own JSON line: that design's prefill and
+                                                                                  decode beside the Llama decoder (renitar: beside the
+                                                                                  Fusazen design) at equal size; garodra also has the
+                                                                                  size 2048-looped)
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and context 4096 (a
 "step" is one decode step of the whole batch), timed on the device with CUDA events around
@@ -314,13 +315,40 @@ GEMOSUN_SIZES = {
 }
 
 
+# --design renitar: the Renitar design at sizes that resemble a real model's layers, beside the Fusazen design (the
+# closest of the library's models: a recurrence with a decay per key channel, attention masked to blocks of positions
+# with whole-row q and k norms, a short convolution) at equal width and depth.  Eight layers: linear attention with a
+# decay per key channel, then two mixers side by side (attention with a convolution on q, k, v, capped scores and a gate
+# per output entry; linear attention with a decay per head), and so on in turn; every layer has routed experts (eight
+# with matrices and two that hand their input on, three a token, a gated shared expert).  The attention's blocks of
+# positions span the whole context of the decode runs, so that it reads as many positions as the other model's.
+def renitar_config(width, heads, kv_heads, dim, r_heads, experts, identity, top, expert_ff, shared, vocab, block, layers=8):
+    gla = {"heads": r_heads, "dim": dim, "vdim": dim, "tau": 16.0, "rank": max(16, width // 32)}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "conv": 4, "softcap": 30.0,
+            "mask": {"size": block}, "rot": {"base": 10000.0, "dims": dim // 2}}
+    right = {"heads": r_heads, "dim": dim, "vdim": dim, "decay": [1.0 - 2.0 ** (-1.0 - 7.0 * h / max(r_heads - 1, 1)) for h in range(r_heads)]}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "identity": identity, "top": top, "scale": 1.5},
+           "shared": {"ff": shared}}
+    kinds = [("gla", gla), ("parallel", {"left": left, "right": right})]
+    return {"architecture": "Renitar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "layers": [{"type": kinds[i % 2][0], "mixer": kinds[i % 2][1], "mlp": moe} for i in range(layers)]}
+
+
+RENITAR_SIZES = {
+    # name: (renitar config, the other model's config, the other model's label)
+    "2048": (renitar_config(2048, 32, 8, 64, 32, 8, 2, 3, 2048, 2048, 49152, 8192), FUSAZEN_SIZES["2048"][0], "fusazen"),
+    "1024": (renitar_config(1024, 16, 4, 64, 16, 8, 2, 3, 1024, 1024, 49152, 8192), FUSAZEN_SIZES["1024"][0], "fusazen"),
+}
+
+
 class KernelTimes:
     """Device time per entry point of ops.kernels inside real steps (CUDA events around every call; steps run launch
     by launch while this is on, so the figures are shares of a step, not a benchmark of it)."""
     NAMES = ("embed", "rmsnorm", "swiglu", "linear", "rope_store", "attention", "dyt", "dyt_add", "stream_add", "linear_batched",
              "latent_prepare", "latent_q_rotate", "attention_latent", "delta_step", "delta_finish", "moe_route",
              "moe_experts_streamed", "moe_experts_grouped", "conv_add", "qkv_prepare", "attention_maps", "diff_combine",
-             "gdelta_prepare", "dplr_recurrence", "activate", "layernorm", "depth_mix", "pool_rows", "gate_rows")
+             "gdelta_prepare", "dplr_recurrence", "activate", "layernorm", "depth_mix", "pool_rows", "gate_rows", "tanh_rows",
+             "channel_decay", "rows_silu", "decay_recurrence", "normed_pair", "stream_axpy_norm", "moe_identity_add")
 
     def __init__(self):
         self.spans, self.saved = [], {}
@@ -363,7 +391,7 @@ def design_run(name, steps, warmup, batch, context, tokens, sizes):
     import torch
     import llmi_b200 as L
     from llmi_b200 import SequenceStep
-    tables = {"garodra": DESIGN_SIZES, "fusazen": FUSAZEN_SIZES, "gemosun": GEMOSUN_SIZES}
+    tables = {"garodra": DESIGN_SIZES, "fusazen": FUSAZEN_SIZES, "gemosun": GEMOSUN_SIZES, "renitar": RENITAR_SIZES}
     if name not in tables:
         print(f"bench.py: unknown design {name!r}")
         return 2
@@ -373,11 +401,11 @@ def design_run(name, steps, warmup, batch, context, tokens, sizes):
            "batch": batch, "context": context, "prefill_tokens": tokens, "steps": steps, "warmup": warmup, "peaks": pk_kind,
            "sizes": {}}
     for size in sizes:
-        g_cfg, l_cfg = table[size]
+        g_cfg, l_cfg, *other = table[size]
         if l_cfg is None:
             l_cfg = DESIGN_SIZES[size.split("-")[0]][1]
         row = {}
-        for label, cfg in ((name, g_cfg), ("llama", l_cfg)):
+        for label, cfg in ((name, g_cfg), (other[0] if other else "llama", l_cfg)):
             model = L.random_model(cfg, seed=0, dtype="bfloat16", on_device=True)
             pre_ms = prefill_run(model, tokens, iters=3)
             ms, launches, _, _, cache_bytes = decode_run(model, batch, context, steps, warmup)
@@ -434,8 +462,8 @@ def main():
     ap.add_argument("--kv-heads", type=int, default=None,
                     help="with --only: another number of key/value heads (grouped queries), to profile their kernels")
     ap.add_argument("--design", default=None,
-                    help="'garodra', 'fusazen' or 'gemosun': that design's prefill and decode throughput at layer sizes of a real model, beside the "
-                         "Llama decoder at equal size (its own JSON line; the default workload is untouched)")
+                    help="'garodra', 'fusazen', 'gemosun' or 'renitar': that design's prefill and decode throughput at layer sizes of a real model, beside the "
+                         "Llama decoder (renitar: beside the Fusazen design) at equal size (its own JSON line; the default workload is untouched)")
     ap.add_argument("--design-sizes", default="2048,1024", help="with --design: which of " + ", ".join(sorted(set(DESIGN_SIZES) | set(GEMOSUN_SIZES))))
     args = ap.parse_args()
 

@@ -25,22 +25,37 @@ namespace llmi {
 __device__ __forceinline__ float log_logistic(float z) { return z < 0.f ? z - log1pf(expf(z)) : -log1pf(expf(-z)); }
 
 // `low` fp32 rows [T, ld] (R entries from column 0 of the pointer); w2t fp32 [R, H*D] (the second matrix transposed:
-// neighbouring threads read neighbours); bias fp32 [H*D]; dec fp32 [T, ldd] receives the decays.
+// neighbouring threads read neighbours); bias fp32 [H*D]; dec fp32 [T, ldd] receives the decays.  A block takes
+// DECAY_PREP_TOK tokens and blockDim.x channels: an entry of w2t is read once for all of the block's tokens; a token's
+// sum runs over j in ascending order whatever tokens share its block.
+constexpr int DECAY_PREP_TOK = 8;
 __global__ void __launch_bounds__(256)
 channel_decay_kernel(const float* __restrict__ low, long ld, int R, const float* __restrict__ w2t, const float* __restrict__ bias,
-                     float inv_tau, int N, const int32_t* __restrict__ tok_seq, float* __restrict__ dec, long ldd) {
-  extern __shared__ float low_s[];
+                     float inv_tau, int N, int n_tokens, const int32_t* __restrict__ tok_seq, float* __restrict__ dec, long ldd) {
+  extern __shared__ float low_s[];                           // [DECAY_PREP_TOK][R]
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x;
-  if (tok_seq[t] < 0) return;
-  for (int j = threadIdx.x; j < R; j += blockDim.x) low_s[j] = low[(size_t)t * ld + j];
-  __syncthreads();
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < N; c += gridDim.y * blockDim.x) {
-    float z = bias ? bias[c] : 0.f;
-    for (int j = 0; j < R; ++j) z = fmaf(w2t[(size_t)j * N + c], low_s[j], z);
-    dec[(size_t)t * ldd + c] = expf(log_logistic(z) * inv_tau);
+  const int t0 = blockIdx.x * DECAY_PREP_TOK, cnt = min(DECAY_PREP_TOK, n_tokens - t0);
+  for (int x = threadIdx.x; x < cnt * R; x += blockDim.x) {
+    const int tt = x / R, j = x - tt * R;
+    low_s[x] = low[(size_t)(t0 + tt) * ld + j];
   }
+  __syncthreads();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= N) return;
+  float z[DECAY_PREP_TOK];
+  const float b = bias ? bias[c] : 0.f;
+#pragma unroll
+  for (int tt = 0; tt < DECAY_PREP_TOK; ++tt) z[tt] = b;
+  for (int j = 0; j < R; ++j) {
+    const float w = w2t[(size_t)j * N + c];
+#pragma unroll
+    for (int tt = 0; tt < DECAY_PREP_TOK; ++tt)
+      if (tt < cnt) z[tt] = fmaf(w, low_s[tt * R + j], z[tt]);
+  }
+#pragma unroll
+  for (int tt = 0; tt < DECAY_PREP_TOK; ++tt)
+    if (tt < cnt && tok_seq[t0 + tt] >= 0) dec[(size_t)(t0 + tt) * ldd + c] = expf(log_logistic(z[tt]) * inv_tau);
 }
 
 // x[t, 0:n] = act(x[t, 0:n]) in place; act 0: silu.
@@ -53,6 +68,23 @@ rows_activate_kernel(float* __restrict__ x, long ld, int n, long total, int act)
     float* p = x + t * ld + (i - t * n);
     const float v = *p;
     *p = v / (1.0f + expf(-v));
+  }
+}
+
+// The same for rows of whole 16-byte pieces: n4 = n / 4 pieces a row.
+__global__ void __launch_bounds__(256)
+rows_activate_vec4_kernel(float* __restrict__ x, long ld, int n4, long total4, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / n4;
+    float4* p = reinterpret_cast<float4*>(x + t * ld) + (i - t * n4);
+    float4 v = *p;
+    v.x = v.x / (1.0f + expf(-v.x));
+    v.y = v.y / (1.0f + expf(-v.y));
+    v.z = v.z / (1.0f + expf(-v.z));
+    v.w = v.w / (1.0f + expf(-v.w));
+    *p = v;
   }
 }
 
@@ -123,12 +155,15 @@ decay_recurrence_kernel(DecaySources a, int H, int D, int Dv, float* __restrict_
 
 // The form for D a multiple of 4 up to 128 and Dv a multiple of 16.  A thread holds TWO neighbouring columns of S and
 // a sixteenth of their entries (lane `sub` of sixteen: d = 64 i + 4 sub + 0..3, while d < D) in registers; the partial
-// sums of o over d are joined by four shuffles, one token late, off the chain from token to token.  A head's columns
-// are cut into slices of 32 (or 16), every slice a block of its own (blockIdx.z), and what a token needs — w (unless
-// the decay is a number per head), k, q of the head, the slice's v — is copied into a ring of DECAY_RING entries
-// DECAY_RING - 1 tokens ahead (cp.async, 16 bytes a copy), so that no load's latency lies on the chain; one barrier
-// per token.
-constexpr int DECAY_RING = 8;
+// sums of o over d of a stage's eight tokens (sixteen numbers a thread) are joined over the sixteen lanes at the stage's
+// end by a butterfly that halves what a lane keeps in every round (fifteen shuffles for eight tokens; lane i ends up
+// with number i: token i / 2, column i % 2), off the chain from token to token.  A head's columns
+// are cut into slices of 32 (or 16), every slice a block of its own (blockIdx.z).  What the tokens need — w (unless the
+// decay is a number per head), k, q of the head, the slice's v — is copied into a ring of DECAY_RING stages of
+// DECAY_TOK tokens each, DECAY_RING - 1 stages ahead (cp.async, 16 bytes a copy), so that no load's latency lies on the
+// chain; ONE barrier per stage: nothing on the chain from token to token needs another thread (a token is two dependent
+// operations per state entry), so a barrier per token would be most of a token's time.
+constexpr int DECAY_RING = 4, DECAY_TOK = 8;      // (eight tokens x two columns = the sixteen lanes of the butterfly)
 
 __device__ __forceinline__ void decay_cp16(void* dst, const void* src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -166,7 +201,7 @@ decay_recurrence_lanes_kernel(DecaySources a, int H, int D, int Dv, float* __res
     S_r[i][2] = make_float2(c0.z, c1.z);
     S_r[i][3] = make_float2(c0.w, c1.w);
   }
-  // ring entry: [w (D, unless SCALAR) | k (D) | q (D) | v of the slice (CB)]; all parts are whole 16-byte pieces
+  // a token's entry of a stage: [w (D, unless SCALAR) | k (D) | q (D) | v of the slice (CB)]; all parts are whole 16-byte pieces
   constexpr int NVEC = SCALAR ? 2 : 3;
   const int Q = D / 4;                                       // 16-byte pieces of one vector
   const int n16 = NVEC * Q + CB / 4, pitch = NVEC * D + CB;
@@ -174,70 +209,94 @@ decay_recurrence_lanes_kernel(DecaySources a, int H, int D, int Dv, float* __res
   const float* k_src = a.proj + a.k_off + (size_t)h * D;
   const float* q_src = a.proj + a.q_off + (size_t)h * D;
   const float* w_src = SCALAR ? nullptr : a.dec + (size_t)h * D;
-  auto issue = [&](int i) {
-    float* dst = sm + (size_t)(i % DECAY_RING) * pitch;
-    const size_t xrow = (size_t)(r0 + i) * a.ld;
-    for (int e = threadIdx.x; e < n16; e += blockDim.x) {
-      const int part = e / Q, off = 4 * (e - part * Q);
-      const int which = SCALAR ? part + 1 : part;            // 0: w, 1: k, 2: q, 3: v
-      if (which == 0) decay_cp16(dst + 4 * e, w_src + (size_t)(r0 + i) * a.ldw + off);
-      else if (which == 1) decay_cp16(dst + 4 * e, k_src + xrow + off);
-      else if (which == 2) decay_cp16(dst + 4 * e, q_src + xrow + off);
-      else decay_cp16(dst + 4 * e, v_src + xrow + 4 * (e - NVEC * Q));
-    }
+  const int n_stages = (n + DECAY_TOK - 1) / DECAY_TOK;
+  // a token's entry has at most 3 * 32 + 8 pieces, fewer than the block has threads: thread e copies piece e of every
+  // token, from an address that moves by one row a token
+  const float* my_src = nullptr;
+  long my_step = 0;
+  if ((int)threadIdx.x < n16) {
+    const int e = threadIdx.x, part = e / Q, off = 4 * (e - part * Q);
+    const int which = SCALAR ? part + 1 : part;              // 0: w, 1: k, 2: q, 3: v
+    my_step = which == 0 ? a.ldw : a.ld;
+    my_src = (which == 0 ? w_src + off : which == 1 ? k_src + off : which == 2 ? q_src + off : v_src + 4 * (e - NVEC * Q)) +
+             (size_t)r0 * my_step;
+  }
+  auto issue = [&](int st) {
+    if (!my_src) return;
+    float* dst = sm + (size_t)(st % DECAY_RING) * DECAY_TOK * pitch + 4 * threadIdx.x;
+    const int t0 = st * DECAY_TOK, cnt = min(DECAY_TOK, n - t0);
+    const float* src = my_src + (size_t)t0 * my_step;
+#pragma unroll
+    for (int tk = 0; tk < DECAY_TOK; ++tk)
+      if (tk < cnt) decay_cp16(dst + (size_t)tk * pitch, src + (size_t)tk * my_step);
   };
 #pragma unroll
   for (int s = 0; s < DECAY_RING - 1; ++s) {
-    if (s < n) issue(s);
+    if (s < n_stages) issue(s);
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
   const float wh = SCALAR ? a.head_decay[h] : 0.f;
-  float2 o_pend = make_float2(0.f, 0.f);                       // my part of the token before's S . q
-  for (int i = 0; i < n; ++i) {
+  float* o_dst = o_raw + (size_t)r0 * ldo + (size_t)h * Dv + col0;
+  for (int st = 0; st < n_stages; ++st) {
     asm volatile("cp.async.wait_group %0;" ::"n"(DECAY_RING - 2) : "memory");
-    __syncthreads();                                         // token i's entry is there; token i-1's entry is read out
-    if (i + DECAY_RING - 1 < n) issue(i + DECAY_RING - 1);
+    __syncthreads();                                         // stage st is there; stage st-1 is read out
+    if (st + DECAY_RING - 1 < n_stages) issue(st + DECAY_RING - 1);
     asm volatile("cp.async.commit_group;" ::: "memory");
-    const float* in = sm + (size_t)(i % DECAY_RING) * pitch;
+    const float* stage = sm + (size_t)(st % DECAY_RING) * DECAY_TOK * pitch;
+    const int t0 = st * DECAY_TOK, cnt = min(DECAY_TOK, n - t0);
+    float part[2 * DECAY_TOK];                               // my part of S . q: [token][column]
+    auto token = [&](const float* in, float& p0, float& p1) {
+      const float2 v = *reinterpret_cast<const float2*>(in + NVEC * D + 2 * cg);
+      float2 o2 = make_float2(0.f, 0.f), o3 = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int o = 1; o < 16; o <<= 1) {                         // the token before's read-out, joined over the sixteen lanes
-      o_pend.x += __shfl_xor_sync(0xffffffffu, o_pend.x, o);
-      o_pend.y += __shfl_xor_sync(0xffffffffu, o_pend.y, o);
-    }
-    if (i > 0 && sub == 0)
-      *reinterpret_cast<float2*>(o_raw + (size_t)(r0 + i - 1) * ldo + (size_t)h * Dv + col0) = make_float2(o_pend.x * a.q_scale, o_pend.y * a.q_scale);
-    const float2 v = *reinterpret_cast<const float2*>(in + NVEC * D + 2 * cg);
-    float2 o2 = make_float2(0.f, 0.f), o3 = make_float2(0.f, 0.f);
+      for (int c = 0; c < NI; ++c) {
+        const float4 ww = SCALAR ? make_float4(wh, wh, wh, wh) : (holds[c] ? *reinterpret_cast<const float4*>(in + 64 * c + 4 * sub) : zero);
+        const float4 kk = holds[c] ? *reinterpret_cast<const float4*>(in + (NVEC - 2) * D + 64 * c + 4 * sub) : zero;
+        const float4 qq = holds[c] ? *reinterpret_cast<const float4*>(in + (NVEC - 1) * D + 64 * c + 4 * sub) : zero;
+        const float we[4] = {ww.x, ww.y, ww.z, ww.w}, ke[4] = {kk.x, kk.y, kk.z, kk.w}, qe[4] = {qq.x, qq.y, qq.z, qq.w};
 #pragma unroll
-    for (int c = 0; c < NI; ++c) {
-      const float4 ww = SCALAR ? make_float4(wh, wh, wh, wh) : (holds[c] ? *reinterpret_cast<const float4*>(in + 64 * c + 4 * sub) : zero);
-      const float4 kk = holds[c] ? *reinterpret_cast<const float4*>(in + (NVEC - 2) * D + 64 * c + 4 * sub) : zero;
-      const float4 qq = holds[c] ? *reinterpret_cast<const float4*>(in + (NVEC - 1) * D + 64 * c + 4 * sub) : zero;
-      const float we[4] = {ww.x, ww.y, ww.z, ww.w}, ke[4] = {kk.x, kk.y, kk.z, kk.w}, qe[4] = {qq.x, qq.y, qq.z, qq.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float2 s = S_r[c][e];
-        s.x = fmaf(ke[e], v.x, we[e] * s.x);
-        s.y = fmaf(ke[e], v.y, we[e] * s.y);
-        S_r[c][e] = s;
-        if (e & 1) {
-          o3.x = fmaf(s.x, qe[e], o3.x);
-          o3.y = fmaf(s.y, qe[e], o3.y);
-        } else {
-          o2.x = fmaf(s.x, qe[e], o2.x);
-          o2.y = fmaf(s.y, qe[e], o2.y);
+        for (int e = 0; e < 4; ++e) {
+          float2 s = S_r[c][e];
+          s.x = fmaf(ke[e], v.x, we[e] * s.x);
+          s.y = fmaf(ke[e], v.y, we[e] * s.y);
+          S_r[c][e] = s;
+          if (e & 1) {
+            o3.x = fmaf(s.x, qe[e], o3.x);
+            o3.y = fmaf(s.y, qe[e], o3.y);
+          } else {
+            o2.x = fmaf(s.x, qe[e], o2.x);
+            o2.y = fmaf(s.y, qe[e], o2.y);
+          }
         }
       }
-    }
-    o_pend = make_float2(o2.x + o3.x, o2.y + o3.y);           // joined over the lanes in the next token's rounds
-  }
+      p0 = o2.x + o3.x;
+      p1 = o2.y + o3.y;
+    };
+    if (cnt == DECAY_TOK) {                                  // a whole stage: nothing between its tokens but the chain itself
 #pragma unroll
-  for (int o = 1; o < 16; o <<= 1) {                           // the last token's
-    o_pend.x += __shfl_xor_sync(0xffffffffu, o_pend.x, o);
-    o_pend.y += __shfl_xor_sync(0xffffffffu, o_pend.y, o);
+      for (int tk = 0; tk < DECAY_TOK; ++tk) token(stage + (size_t)tk * pitch, part[2 * tk], part[2 * tk + 1]);
+    } else {
+#pragma unroll
+      for (int tk = 0; tk < DECAY_TOK; ++tk) {
+        part[2 * tk] = 0.f;
+        part[2 * tk + 1] = 0.f;
+        if (tk < cnt) token(stage + (size_t)tk * pitch, part[2 * tk], part[2 * tk + 1]);
+      }
+    }
+    // sixteen numbers a lane, sixteen lanes: every round a lane hands one half of what it holds to its partner and adds
+    // the partner's other half to its own; lane `sub` is left with number `sub`.  Every number's sum has the same shape.
+#pragma unroll
+    for (int off = 8, half = DECAY_TOK; off >= 1; off >>= 1, half >>= 1) {
+      const bool upper = (sub & off) != 0;
+#pragma unroll
+      for (int i = 0; i < half; ++i) {
+        const float send = upper ? part[i] : part[i + half];
+        const float keep = upper ? part[i + half] : part[i];
+        part[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+    if ((sub >> 1) < cnt) o_dst[(size_t)(t0 + (sub >> 1)) * ldo + (sub & 1)] = part[0] * a.q_scale;
   }
-  if (sub == 0)
-    *reinterpret_cast<float2*>(o_raw + (size_t)(r0 + n - 1) * ldo + (size_t)h * Dv + col0) = make_float2(o_pend.x * a.q_scale, o_pend.y * a.q_scale);
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   if (write_state) {
 #pragma unroll
@@ -252,8 +311,16 @@ decay_recurrence_lanes_kernel(DecaySources a, int H, int D, int Dv, float* __res
 template <int NI, bool SCALAR>
 int launch_decay_lanes(const DecaySources& a, int H, int D, int Dv, float* state, long state_stride, const int32_t* seq_q_start,
                        const int32_t* seq_slot, float* o_raw, long ldo, int n_seqs, int write_state, cudaStream_t stream) {
-  const int CB = Dv % 32 == 0 ? 32 : 16;                     // columns per block
-  const size_t smem = (size_t)DECAY_RING * ((SCALAR ? 2 : 3) * D + CB) * sizeof(float);
+  // columns per block: 32, or 16 where that gives the device more blocks than it has SMs to fill (the chain over a
+  // sequence's tokens is what a block's time is, however few columns it holds)
+  const int CB = (Dv % 32 == 0 && (long)H * n_seqs * (Dv / 32) >= 2L * sm_count()) ? 32 : 16;
+  const size_t smem = (size_t)DECAY_RING * DECAY_TOK * ((SCALAR ? 2 : 3) * D + CB) * sizeof(float);
+  static PerDevice<size_t> allowed;
+  if (smem > 48 * 1024 && allowed.here() < smem) {
+    if (cudaFuncSetAttribute(decay_recurrence_lanes_kernel<NI, SCALAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return LLMI_ERR_BAD_SIZE;
+    allowed.here() = smem;
+  }
   return launch_pdl(PDL_ATTENTION, decay_recurrence_lanes_kernel<NI, SCALAR>, dim3(H, n_seqs, Dv / CB), dim3(8 * CB), smem, stream,
                     a, H, D, Dv, state, state_stride, seq_q_start, seq_slot, o_raw, ldo, write_state);
 }
@@ -266,12 +333,19 @@ using namespace llmi;
 // null; dec fp32 [T, ldd]: dec[t, c] = logistic(bias[c] + sum_j w2t[j, c] low[t, j])^(1/tau).
 LLMI_EXPORT int llmi_channel_decay(const float* low, long ld, int R, const float* w2t, const float* bias, float tau, int N,
                                    const int32_t* tok_seq, float* dec, long ldd, int n_tokens, cudaStream_t stream) {
-  if (n_tokens <= 0 || N <= 0 || R <= 0 || R > 8192 || !(tau > 0.f)) return LLMI_ERR_BAD_SIZE;
+  if (n_tokens <= 0 || N <= 0 || R <= 0 || R > 4096 || !(tau > 0.f)) return LLMI_ERR_BAD_SIZE;
   const int threads = N >= 256 ? 256 : (N + 31) / 32 * 32;
-  int cuts = (N + threads - 1) / threads;
-  if (n_tokens >= 1024 && cuts > 2) cuts = 2;                // many tokens: fewer blocks each walking more channels
-  return launch_pdl(PDL_SMALL, channel_decay_kernel, dim3(n_tokens, cuts), dim3(threads), (size_t)R * sizeof(float), stream, low, ld,
-                    R, w2t, bias, 1.0f / tau, N, tok_seq, dec, ldd);
+  const int cuts = (N + threads - 1) / threads;
+  if (cuts > 65535) return LLMI_ERR_BAD_SIZE;
+  const size_t smem = (size_t)DECAY_PREP_TOK * R * sizeof(float);
+  static PerDevice<size_t> allowed;
+  if (smem > 48 * 1024 && allowed.here() < smem) {
+    if (cudaFuncSetAttribute(channel_decay_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return LLMI_ERR_BAD_SIZE;
+    allowed.here() = smem;
+  }
+  return launch_pdl(PDL_SMALL, channel_decay_kernel, dim3((n_tokens + DECAY_PREP_TOK - 1) / DECAY_PREP_TOK, cuts), dim3(threads),
+                    smem, stream, low, ld, R, w2t, bias, 1.0f / tau, N, n_tokens, tok_seq, dec, ldd);
 }
 
 // x fp32 [T, ld]: x[:, 0:n] = act(x[:, 0:n]) in place; act 0: silu.
@@ -279,7 +353,13 @@ LLMI_EXPORT int llmi_rows_activate(float* x, long ld, int n, int n_rows, int act
   if (n_rows <= 0 || n <= 0 || ld < n) return LLMI_ERR_BAD_SIZE;
   if (act != 0) return LLMI_ERR_UNSUPPORTED;
   const long total = (long)n_rows * n;
-  const long want = (total + 255) / 256, most = (long)sm_count() * 16;
+  const long most = (long)sm_count() * 16;
+  if (n % 4 == 0 && ld % 4 == 0 && !((uintptr_t)x & 15)) {
+    const long want4 = (total / 4 + 255) / 256;
+    return launch_pdl(PDL_SMALL, rows_activate_vec4_kernel, dim3((unsigned)(want4 < most ? want4 : most)), dim3(256), 0, stream, x,
+                      ld, n / 4, total / 4, act);
+  }
+  const long want = (total + 255) / 256;
   return launch_pdl(PDL_SMALL, rows_activate_kernel, dim3((unsigned)(want < most ? want : most)), dim3(256), 0, stream, x, ld, n,
                     total, act);
 }

@@ -392,6 +392,31 @@ delta_finish_kernel(const float* __restrict__ o_raw, long ldo, const float* __re
     dst[d] = from_f32<T>(w[d] * (o[d] * sc) * (gate_act == 0 ? silu_f(g[d]) : 1.0f / (1.0f + expf(-g[d]))));
 }
 
+// The same for ONE wide "head" per token (a norm over a whole row of many entries): a block per token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_finish_row_kernel(const float* __restrict__ o_raw, long ldo, const float* __restrict__ gate, long ldg,
+                        const float* __restrict__ w, int gate_act, float eps, int Dv, const int32_t* __restrict__ tok_seq,
+                        T* __restrict__ out, long ld_out) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  T* dst = out + (size_t)t * ld_out;
+  if (tok_seq[t] < 0) {
+    for (int d = threadIdx.x; d < Dv; d += blockDim.x) dst[d] = from_f32<T>(0.f);
+    return;
+  }
+  const float* o = o_raw + (size_t)t * ldo;
+  const float* g = gate + (size_t)t * ldg;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < Dv; d += blockDim.x) ss = fmaf(o[d], o[d], ss);
+  ss = block_sum(ss, scratch);
+  const float sc = 1.0f / sqrtf(ss / (float)Dv + eps);
+  for (int d = threadIdx.x; d < Dv; d += blockDim.x)
+    dst[d] = from_f32<T>(w[d] * (o[d] * sc) * (gate_act == 0 ? silu_f(g[d]) : 1.0f / (1.0f + expf(-g[d]))));
+}
+
 template <int DREG>
 int launch_delta_recurrence(const float* prep, long ldp, DeltaDims m, float* state, const int32_t* seq_q_start,
                             const int32_t* seq_slot, float* o_raw, long ldo, int n_seqs, int write_state,
@@ -466,6 +491,15 @@ LLMI_EXPORT int llmi_delta_finish(int dtype, const float* o_raw, long ldo, const
   if (gate_act != 0 && gate_act != 1) return LLMI_ERR_UNSUPPORTED;
   const long items = (long)n_tokens * H;
   const unsigned blocks = (unsigned)((items + 3) / 4);
+  if (H == 1 && Dv >= 512) {
+    if (dtype == LLMI_DTYPE_F32)
+      return launch_pdl(PDL_SMALL, delta_finish_row_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, o_raw, ldo, gate, ldg, w,
+                        gate_act, eps, Dv, tok_seq, (float*)out, ld_out);
+    if (dtype == LLMI_DTYPE_BF16)
+      return launch_pdl(PDL_SMALL, delta_finish_row_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, o_raw, ldo, gate,
+                        ldg, w, gate_act, eps, Dv, tok_seq, (__nv_bfloat16*)out, ld_out);
+    return LLMI_ERR_BAD_DTYPE;
+  }
   if (dtype == LLMI_DTYPE_F32)
     return launch_pdl(PDL_SMALL, delta_finish_kernel<float>, blocks, 128, 0, stream, o_raw, ldo, gate, ldg, w, w_head_stride,
                       gate_act, eps, H, Dv, tok_seq, (float*)out, ld_out, items);
