@@ -10,6 +10,17 @@
 
 namespace llmi {
 
+__device__ __forceinline__ void store4(float* o, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* o, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&lo);
+  u.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(o) = u;
+}
+
 __global__ void __launch_bounds__(256)
 normed_pair_kernel(const float* __restrict__ a, long lda, const float* __restrict__ wa, const float* __restrict__ b, long ldb,
                    const float* __restrict__ wb, float eps, float coeff, float* __restrict__ y, long ldy, int W, int add) {
@@ -46,16 +57,33 @@ stream_axpy_norm_kernel(float* __restrict__ x, const float* __restrict__ y, floa
   float* xr = x + (size_t)t * W;
   const float* yr = y + (size_t)t * W;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float v = fmaf(m, yr[i], xr[i]);
-    xr[i] = v;
-    ss = fmaf(v, v, ss);
+  if (W % 4 == 0) {          // rows of whole 16-byte pieces (x, y are contiguous: every row starts on one)
+    for (int i = threadIdx.x; i < W / 4; i += blockDim.x) {
+      float4 v = reinterpret_cast<const float4*>(xr)[i];
+      const float4 u = reinterpret_cast<const float4*>(yr)[i];
+      v.x = fmaf(m, u.x, v.x); v.y = fmaf(m, u.y, v.y); v.z = fmaf(m, u.z, v.z); v.w = fmaf(m, u.w, v.w);
+      reinterpret_cast<float4*>(xr)[i] = v;
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float v = fmaf(m, yr[i], xr[i]);
+      xr[i] = v;
+      ss = fmaf(v, v, ss);
+    }
   }
   if (!norm_w) return;
   ss = block_sum(ss, scratch);
   const float scale = 1.0f / sqrtf(ss / (float)W + eps);
   T* hr = h + (size_t)t * W;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) hr[i] = from_f32<T>(norm_w[i] * (xr[i] * scale));     // (my own writes above)
+  if (W % 4 == 0) {
+    for (int i = threadIdx.x; i < W / 4; i += blockDim.x) {          // (my own writes above)
+      const float4 v = reinterpret_cast<const float4*>(xr)[i], w = reinterpret_cast<const float4*>(norm_w)[i];
+      store4(hr + 4 * i, w.x * (v.x * scale), w.y * (v.y * scale), w.z * (v.z * scale), w.w * (v.w * scale));
+    }
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) hr[i] = from_f32<T>(norm_w[i] * (xr[i] * scale));
+  }
 }
 
 }  // namespace llmi
@@ -76,6 +104,7 @@ LLMI_EXPORT int llmi_normed_pair(const float* a, long lda, const float* wa, cons
 LLMI_EXPORT int llmi_stream_axpy_norm(float* x, const float* y, float m, int n_rows, int W, const float* norm_w, float eps,
                                       int dtype, void* h, cudaStream_t stream) {
   if (n_rows <= 0 || W <= 0 || (norm_w && !h)) return LLMI_ERR_BAD_SIZE;
+  if (W % 4 == 0 && (((uintptr_t)x & 15) || ((uintptr_t)y & 15) || ((uintptr_t)norm_w & 15) || ((uintptr_t)h & 15))) return LLMI_ERR_ALIGN;
   const int threads = W >= 1024 ? 256 : (W >= 256 ? 128 : 64);
   if (!norm_w || dtype == LLMI_DTYPE_F32)
     return launch_pdl(PDL_SMALL, stream_axpy_norm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, y, m, W, norm_w, eps,

@@ -29,13 +29,14 @@ __device__ __forceinline__ float log_logistic(float z) { return z < 0.f ? z - lo
 // DECAY_PREP_TOK tokens and blockDim.x channels: an entry of w2t is read once for all of the block's tokens; a token's
 // sum runs over j in ascending order whatever tokens share its block.
 constexpr int DECAY_PREP_TOK = 8;
+template <int TOKS>
 __global__ void __launch_bounds__(256)
 channel_decay_kernel(const float* __restrict__ low, long ld, int R, const float* __restrict__ w2t, const float* __restrict__ bias,
                      float inv_tau, int N, int n_tokens, const int32_t* __restrict__ tok_seq, float* __restrict__ dec, long ldd) {
-  extern __shared__ float low_s[];                           // [DECAY_PREP_TOK][R]
+  extern __shared__ float low_s[];                           // [TOKS][R]
   pdl_launch_dependents();
   pdl_wait();
-  const int t0 = blockIdx.x * DECAY_PREP_TOK, cnt = min(DECAY_PREP_TOK, n_tokens - t0);
+  const int t0 = blockIdx.x * TOKS, cnt = min(TOKS, n_tokens - t0);
   for (int x = threadIdx.x; x < cnt * R; x += blockDim.x) {
     const int tt = x / R, j = x - tt * R;
     low_s[x] = low[(size_t)(t0 + tt) * ld + j];
@@ -43,18 +44,19 @@ channel_decay_kernel(const float* __restrict__ low, long ld, int R, const float*
   __syncthreads();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= N) return;
-  float z[DECAY_PREP_TOK];
+  float z[TOKS];
   const float b = bias ? bias[c] : 0.f;
 #pragma unroll
-  for (int tt = 0; tt < DECAY_PREP_TOK; ++tt) z[tt] = b;
+  for (int tt = 0; tt < TOKS; ++tt) z[tt] = b;
+#pragma unroll 8
   for (int j = 0; j < R; ++j) {
     const float w = w2t[(size_t)j * N + c];
 #pragma unroll
-    for (int tt = 0; tt < DECAY_PREP_TOK; ++tt)
+    for (int tt = 0; tt < TOKS; ++tt)
       if (tt < cnt) z[tt] = fmaf(w, low_s[tt * R + j], z[tt]);
   }
 #pragma unroll
-  for (int tt = 0; tt < DECAY_PREP_TOK; ++tt)
+  for (int tt = 0; tt < TOKS; ++tt)
     if (tt < cnt && tok_seq[t0 + tt] >= 0) dec[(size_t)(t0 + tt) * ldd + c] = expf(log_logistic(z[tt]) * inv_tau);
 }
 
@@ -334,18 +336,25 @@ using namespace llmi;
 LLMI_EXPORT int llmi_channel_decay(const float* low, long ld, int R, const float* w2t, const float* bias, float tau, int N,
                                    const int32_t* tok_seq, float* dec, long ldd, int n_tokens, cudaStream_t stream) {
   if (n_tokens <= 0 || N <= 0 || R <= 0 || R > 4096 || !(tau > 0.f)) return LLMI_ERR_BAD_SIZE;
+  if (n_tokens <= 64) {        // a handful of tokens: a block per token and 64 channels, so that the device has blocks enough
+    const int threads = N >= 64 ? 64 : (N + 31) / 32 * 32;
+    const int cuts = (N + threads - 1) / threads;
+    if (cuts > 65535) return LLMI_ERR_BAD_SIZE;
+    return launch_pdl(PDL_SMALL, channel_decay_kernel<1>, dim3(n_tokens, cuts), dim3(threads), (size_t)R * sizeof(float), stream,
+                      low, ld, R, w2t, bias, 1.0f / tau, N, n_tokens, tok_seq, dec, ldd);
+  }
   const int threads = N >= 256 ? 256 : (N + 31) / 32 * 32;
   const int cuts = (N + threads - 1) / threads;
   if (cuts > 65535) return LLMI_ERR_BAD_SIZE;
   const size_t smem = (size_t)DECAY_PREP_TOK * R * sizeof(float);
   static PerDevice<size_t> allowed;
   if (smem > 48 * 1024 && allowed.here() < smem) {
-    if (cudaFuncSetAttribute(channel_decay_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(channel_decay_kernel<DECAY_PREP_TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return LLMI_ERR_BAD_SIZE;
     allowed.here() = smem;
   }
-  return launch_pdl(PDL_SMALL, channel_decay_kernel, dim3((n_tokens + DECAY_PREP_TOK - 1) / DECAY_PREP_TOK, cuts), dim3(threads),
-                    smem, stream, low, ld, R, w2t, bias, 1.0f / tau, N, n_tokens, tok_seq, dec, ldd);
+  return launch_pdl(PDL_SMALL, channel_decay_kernel<DECAY_PREP_TOK>, dim3((n_tokens + DECAY_PREP_TOK - 1) / DECAY_PREP_TOK, cuts),
+                    dim3(threads), smem, stream, low, ld, R, w2t, bias, 1.0f / tau, N, n_tokens, tok_seq, dec, ldd);
 }
 
 // x fp32 [T, ld]: x[:, 0:n] = act(x[:, 0:n]) in place; act 0: silu.

@@ -216,16 +216,19 @@ moe_grouped_kernel(const __nv_bfloat16* __restrict__ A, long lda, const int32_t*
 // One block per token: y[t] = sum_j wt[t, j] * ys[item_pos[t * top + j]] in the order of j.
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ ys, const int32_t* __restrict__ item_pos, const float* __restrict__ wt, int top,
-                   int W, float* __restrict__ y, long ldy, int add) {
+                   int W, float* __restrict__ y, long ldy, int add, const __nv_bfloat16* __restrict__ h, long ldh,
+                   const float* __restrict__ id_wt) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+  const float idw = id_wt ? id_wt[t] : 0.f;          // what the token's chosen experts that hand their input on weigh together
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
     float total = 0.f;
     for (int j = 0; j < top; ++j) {
       const int pos = item_pos[(size_t)t * top + j];
       if (pos >= 0) total = fmaf(wt[(size_t)t * top + j], ys[(size_t)pos * W + c], total);
     }
+    if (idw != 0.f) total = fmaf(idw, __bfloat162float(h[(size_t)t * ldh + c]), total);
     y[(size_t)t * ldy + c] = add ? y[(size_t)t * ldy + c] + total : total;
   }
 }
@@ -441,10 +444,12 @@ LLMI_EXPORT long llmi_moe_group_ints(int n_items, int E) {
   return (E + 1) + 2L * n_items + 2 * max_tiles + 1;
 }
 
+// id_wt (optional, fp32 [n_tokens]): a token's summed weight of chosen experts that hand their input on (choices of
+// index -1): id_wt[t] * h[t] joins the token's sum in the kernel that forms it.
 LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const void* wu, const void* wd, int W, int F, int E,
                                  int top, const int32_t* idx, const float* wt, int act, int32_t* scratch, long scratch_ints,
                                  void* a_sorted, float* y_sorted, float* y, long ldy, int n_tokens, int add, void* h_sorted,
-                                 int* error_flag, cudaStream_t stream) {
+                                 int* error_flag, const float* id_wt, cudaStream_t stream) {
   if (n_tokens <= 0 || W <= 0 || F <= 0 || E <= 0 || E > 256 || top <= 0) return LLMI_ERR_BAD_SIZE;
   if ((W % 8) || (F % 8) || (ldh % 8) || ((uintptr_t)h & 15) || ((uintptr_t)wg & 15) || ((uintptr_t)wu & 15) || ((uintptr_t)wd & 15) ||
       ((uintptr_t)a_sorted & 15))
@@ -452,6 +457,8 @@ LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const 
   if (act < 0 || act > 3 || (act >= 2 && wg)) return LLMI_ERR_UNSUPPORTED;
   const int n_items = n_tokens * top;
   if (scratch_ints < llmi_moe_group_ints(n_items, E)) return LLMI_ERR_BAD_SIZE;
+  // the weighted sum of a token's choices: a handful of tokens spread their columns over several blocks
+  const int combine_cuts = n_tokens >= 64 ? 1 : (W + 255) / 256 < 32 ? (W + 255) / 256 : 32;
   const int max_tiles = (n_items + GB_M - 1) / GB_M + E;
   int32_t* offsets = scratch;
   int32_t* sorted_items = offsets + (E + 1);
@@ -496,8 +503,8 @@ LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const 
     rc = launch_pdl(PDL_GEMM, moe_grouped_tc_kernel, dim3((unsigned)min((long)tiles_most * mt_down, sms)), dim3(TC_THREADS),
                     (size_t)GT_SMEM, stream, mw_down, mx_down, pd, mt_down);
     if (rc != LLMI_OK) return rc;
-    return launch_pdl(PDL_SMALL, moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)y_sorted,
-                      (const int32_t*)item_pos, wt, top, W, y, ldy, add);
+    return launch_pdl(PDL_SMALL, moe_combine_kernel, dim3(n_tokens, combine_cuts), dim3(256), 0, stream, (const float*)y_sorted,
+                      (const int32_t*)item_pos, wt, top, W, y, ldy, add, (const __nv_bfloat16*)h, ldh, id_wt);
   }
   const size_t smem_up = (size_t)GB_STAGES * 3 * GB_M * GB_LD * 2, smem_down = (size_t)GB_STAGES * 2 * GB_M * GB_LD * 2;
   const __nv_bfloat16* hb = (const __nv_bfloat16*)h;
@@ -535,8 +542,8 @@ LLMI_EXPORT int llmi_moe_grouped(const void* h, long ldh, const void* wg, const 
                   (const int32_t*)sorted_items, top, d, d, W, F, (const int32_t*)offsets, (const int32_t*)tile_expert,
                   (const int32_t*)tile_row0, (const int32_t*)n_tiles, (void*)y_sorted, (long)W, 0, 0L, 0L);
   if (rc != LLMI_OK) return rc;
-  return launch_pdl(PDL_SMALL, moe_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)y_sorted,
-                    (const int32_t*)item_pos, wt, top, W, y, ldy, add);
+  return launch_pdl(PDL_SMALL, moe_combine_kernel, dim3(n_tokens, combine_cuts), dim3(256), 0, stream, (const float*)y_sorted,
+                    (const int32_t*)item_pos, wt, top, W, y, ldy, add, (const __nv_bfloat16*)h, ldh, id_wt);
 }
 
 // `batch` products of equal sizes on the tensor cores (bf16), one per head: out[:, b*by : b*by+N] = x[:, b*bx : b*bx+K] . w[b]^T,

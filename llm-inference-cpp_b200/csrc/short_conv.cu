@@ -104,6 +104,42 @@ conv_add_vec8_kernel(const __nv_bfloat16* __restrict__ h, long ldh, const float*
   *reinterpret_cast<uint4*>(y + (size_t)t * ldy + c) = outv;
 }
 
+// The convolution alone (the input itself is not added) on fp32 rows whose channels come in whole groups of four
+// (16-byte accesses): one thread per (token, four channels); the sums and their order are those of conv_add_kernel.
+__global__ void __launch_bounds__(128)
+conv_vec4_kernel(const float* __restrict__ h, long ldh, const float* __restrict__ w, const float* __restrict__ carry_all,
+                 long carry_stride, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos,
+                 const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_slot, float* __restrict__ y, long ldy,
+                 int C, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (c >= C) return;
+  const int seq = tok_seq[t];
+  if (seq < 0) {
+    *reinterpret_cast<float4*>(y + (size_t)t * ldy + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+    return;
+  }
+  const int slot = seq_slot[seq];
+  const int pos = tok_pos[t], r0 = seq_q_start[seq];
+  const int p0 = pos - (t - r0);
+  const float* carry = carry_all + (size_t)(slot < 0 ? 0 : slot) * carry_stride;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j = 0; j < K; ++j) {                               // oldest tap first
+    const int p = pos - (K - 1) + j;
+    if (p < 0) continue;
+    const float4 x = p >= p0 ? *reinterpret_cast<const float4*>(h + (size_t)(r0 + (p - p0)) * ldh + c)
+                             : *reinterpret_cast<const float4*>(carry + (size_t)(p - (p0 - (K - 1))) * C + c);
+    const float4 wj = *reinterpret_cast<const float4*>(w + (size_t)j * C + c);
+    acc.x = fmaf(x.x, wj.x, acc.x);
+    acc.y = fmaf(x.y, wj.y, acc.y);
+    acc.z = fmaf(x.z, wj.z, acc.z);
+    acc.w = fmaf(x.w, wj.w, acc.w);
+  }
+  *reinterpret_cast<float4*>(y + (size_t)t * ldy + c) = acc;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 conv_carry_kernel(const T* __restrict__ h, long ldh, float* __restrict__ carry_all, long carry_stride,
@@ -204,6 +240,12 @@ LLMI_EXPORT int llmi_conv_add(int dtype, const void* h, long ldh, const float* w
                               cudaStream_t stream) {
   if (n_tokens <= 0 || C <= 0 || (C + 127) / 128 > 65535 || K < 1 || K > CONV_MAX_TAPS) return LLMI_ERR_BAD_SIZE;
   const dim3 grid(n_tokens, (C + 127) / 128);
+  if (dtype == LLMI_DTYPE_F32 && !add_input && C % 4 == 0 && ldh % 4 == 0 && ldy % 4 == 0 && carry_stride % 4 == 0 &&
+      !((uintptr_t)h & 15) && !((uintptr_t)y & 15) && !((uintptr_t)w & 15) && !((uintptr_t)carry & 15)) {
+    const int threads = C / 4 >= 128 ? 128 : ((C / 4 + 31) / 32) * 32;
+    return launch_pdl(PDL_SMALL, conv_vec4_kernel, dim3(n_tokens, (C / 4 + threads - 1) / threads), dim3(threads), 0, stream,
+                      (const float*)h, ldh, w, carry, carry_stride, tok_seq, tok_pos, seq_q_start, seq_slot, (float*)y, ldy, C, K);
+  }
   if (dtype == LLMI_DTYPE_F32)
     return launch_pdl(PDL_SMALL, conv_add_kernel<float>, grid, dim3(128), 0, stream, (const float*)h, ldh, w, carry, carry_stride,
                       tok_seq, tok_pos, seq_q_start, seq_slot, (float*)y, ldy, C, K, add_input);

@@ -1465,10 +1465,13 @@ def moe_grouped_applies(h: torch.Tensor, W: int, F: int, E: int) -> bool:
                 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0 and not _FORCE_SIMT)
 
 
-def moe_experts_grouped(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int, rt, y: torch.Tensor, add: bool = False) -> None:
+def moe_experts_grouped(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int, rt, y: torch.Tensor, add: bool = False,
+                        id_wt: torch.Tensor | None = None) -> None:
     """The same result as :func:`moe_experts_streamed` for many tokens: the (token, choice) items are grouped by expert
-    and each expert's products run as tensor-core tiles over its rows.  bf16; ``rt`` lends the scratch."""
-    _need_cuda(h, w_gate, w_up, w_down, idx, wt, y)
+    and each expert's products run as tensor-core tiles over its rows.  bf16; ``rt`` lends the scratch.  ``id_wt`` (fp32
+    [T], optional): id_wt[t] * h[t] joins token t's sum (what :func:`moe_identity_add` adds, without a kernel of its own)."""
+    _need_cuda(h, w_gate, w_up, w_down, idx, wt, y, id_wt)
+    assert id_wt is None or (id_wt.dtype == torch.float32 and id_wt.is_contiguous() and id_wt.numel() >= h.shape[0])
     T, W = h.shape
     E, F, _ = w_up.shape
     top = idx.shape[1]
@@ -1485,7 +1488,7 @@ def moe_experts_grouped(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int
     _check("moe_grouped", lib().llmi_moe_grouped(
         _ptr(h), c_long(h.stride(0)), _ptr(w_gate), _ptr(w_up), _ptr(w_down), c_int(W), c_int(F), c_int(E), c_int(top), _ptr(idx),
         _ptr(wt), c_int(act), _ptr(scratch), c_long(n_int), _ptr(a_sorted), _ptr(y_sorted), _ptr(y), c_long(y.stride(0)), c_int(T),
-        c_int(1 if add else 0), _ptr(h_sorted), _ptr(tc_scratch(h.device).error), _stream()))
+        c_int(1 if add else 0), _ptr(h_sorted), _ptr(tc_scratch(h.device).error), _ptr(id_wt), _stream()))
 
 
 # ---------------------------------------------------------------------------------------------

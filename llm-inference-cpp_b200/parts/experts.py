@@ -108,12 +108,13 @@ class RoutedExperts:
         kernels.moe_route(logits, self.top, ctx, idx, wt, self.route_mode, self.n_groups, self.keep, experts=self.n_out,
                           correction=self.correction, scale=self.route_scale, identity=self.identity, id_wt=id_wt)
         if kernels.moe_grouped_applies(h, self.width, self.inner, self.E):
-            kernels.moe_experts_grouped(h, self.w_gate, self.w_up, self.w_down, idx, wt, self.act, rt, x, add=not store)
+            # (what the chosen experts without tensors add — the token's input times their summed weight — joins the sum there)
+            kernels.moe_experts_grouped(h, self.w_gate, self.w_up, self.w_down, idx, wt, self.act, rt, x, add=not store, id_wt=id_wt)
         else:
             a = rt.scratch("experts_act", (T, self.top, self.inner), torch.float32)
             kernels.moe_experts_streamed(h, self.w_gate, self.w_up, self.w_down, idx, wt, self.act, a, x, add=not store)
-        if self.identity:    # what the chosen experts without tensors add: the token's input times their summed weight
-            kernels.moe_identity_add(h, id_wt, x)
+            if self.identity:
+                kernels.moe_identity_add(h, id_wt, x)
         if self.shared:      # every token's expert: x += logistic(z_sg) * W_down act(W_up h); the gate scales the activation rows
             sa = rt.scratch("shared_act", (T, self.shared))
             kernels.linear(h, self.w_shared_up, sa, None, self.plain_act)

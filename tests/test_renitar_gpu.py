@@ -457,12 +457,12 @@ def test_experts_with_the_exact_gelu_on_every_kind_of_tile(T, E, top, W, F):
     idw = (wt * (idx < 0)).sum(1).contiguous()
     y = torch.full((T, W), float("nan"), device="cuda:0")
     act = kernels.EXPERT_ACTIVATIONS["gelu"]
-    if kernels.moe_grouped_applies(h, W, F, E):
-        kernels.moe_experts_grouped(h, None, wu, wd, idx, wt, act, rt, y)
+    if kernels.moe_grouped_applies(h, W, F, E):          # (the grouped form adds the handed-on inputs in the kernel that forms the sum)
+        kernels.moe_experts_grouped(h, None, wu, wd, idx, wt, act, rt, y, id_wt=idw)
     else:
         a = torch.empty((T, top, F), device="cuda:0")
         kernels.moe_experts_streamed(h, None, wu, wd, idx, wt, act, a, y)
-    kernels.moe_identity_add(h, idw, y)
+        kernels.moe_identity_add(h, idw, y)
     kernels.check_device_errors(torch.device("cuda:0"))
     hd = h.double()
     ref = idw.double()[:, None] * hd
