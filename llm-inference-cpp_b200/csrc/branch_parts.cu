@@ -23,26 +23,49 @@ __device__ __forceinline__ void store4(__nv_bfloat16* o, float a, float b, float
 
 __global__ void __launch_bounds__(256)
 normed_pair_kernel(const float* __restrict__ a, long lda, const float* __restrict__ wa, const float* __restrict__ b, long ldb,
-                   const float* __restrict__ wb, float eps, float coeff, float* __restrict__ y, long ldy, int W, int add) {
+                   const float* __restrict__ wb, float eps, float coeff, float* __restrict__ y, long ldy, int W, int add,
+                   int vec4) {
   __shared__ float scratch[32];
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   const float* ar = a + (size_t)t * lda;
   const float* br = b + (size_t)t * ldb;
+  float* yr = y + (size_t)t * ldy;
   float sa = 0.f, sb = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    sa = fmaf(ar[i], ar[i], sa);
-    sb = fmaf(br[i], br[i], sb);
+  if (vec4) {                // rows of whole 16-byte pieces, every row starting on one
+    for (int i = threadIdx.x; i < W / 4; i += blockDim.x) {
+      const float4 p = reinterpret_cast<const float4*>(ar)[i], q = reinterpret_cast<const float4*>(br)[i];
+      sa = fmaf(p.x, p.x, sa); sa = fmaf(p.y, p.y, sa); sa = fmaf(p.z, p.z, sa); sa = fmaf(p.w, p.w, sa);
+      sb = fmaf(q.x, q.x, sb); sb = fmaf(q.y, q.y, sb); sb = fmaf(q.z, q.z, sb); sb = fmaf(q.w, q.w, sb);
+    }
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      sa = fmaf(ar[i], ar[i], sa);
+      sb = fmaf(br[i], br[i], sb);
+    }
   }
   sa = block_sum(sa, scratch);
   __syncthreads();
   sb = block_sum(sb, scratch);
   const float ia = 1.0f / sqrtf(sa / (float)W + eps), ib = 1.0f / sqrtf(sb / (float)W + eps);
-  float* yr = y + (size_t)t * ldy;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float v = coeff * (ar[i] * ia * wa[i] + br[i] * ib * wb[i]);
-    yr[i] = add ? yr[i] + v : v;
+  if (vec4) {
+    for (int i = threadIdx.x; i < W / 4; i += blockDim.x) {
+      const float4 p = reinterpret_cast<const float4*>(ar)[i], q = reinterpret_cast<const float4*>(br)[i];
+      const float4 u = reinterpret_cast<const float4*>(wa)[i], w = reinterpret_cast<const float4*>(wb)[i];
+      float4 v = make_float4(coeff * (p.x * ia * u.x + q.x * ib * w.x), coeff * (p.y * ia * u.y + q.y * ib * w.y),
+                             coeff * (p.z * ia * u.z + q.z * ib * w.z), coeff * (p.w * ia * u.w + q.w * ib * w.w));
+      if (add) {
+        const float4 o = reinterpret_cast<const float4*>(yr)[i];
+        v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+      }
+      reinterpret_cast<float4*>(yr)[i] = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float v = coeff * (ar[i] * ia * wa[i] + br[i] * ib * wb[i]);
+      yr[i] = add ? yr[i] + v : v;
+    }
   }
 }
 
@@ -95,8 +118,10 @@ LLMI_EXPORT int llmi_normed_pair(const float* a, long lda, const float* wa, cons
                                  float coeff, float* y, long ldy, int W, int n_rows, int add, cudaStream_t stream) {
   if (n_rows <= 0 || W <= 0) return LLMI_ERR_BAD_SIZE;
   const int threads = W >= 1024 ? 256 : (W >= 256 ? 128 : 64);
+  const int vec4 = W % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0 && ldy % 4 == 0 && !((uintptr_t)a & 15) && !((uintptr_t)b & 15) &&
+                   !((uintptr_t)y & 15) && !((uintptr_t)wa & 15) && !((uintptr_t)wb & 15);
   return launch_pdl(PDL_SMALL, normed_pair_kernel, dim3(n_rows), dim3(threads), 0, stream, a, lda, wa, b, ldb, wb, eps, coeff, y, ldy,
-                    W, add);
+                    W, add, vec4);
 }
 
 // x, y fp32 [T, W] contiguous: x += m * y.  With norm_w (fp32 [W]): h [T, W] contiguous in `dtype` = the RMS norm of the

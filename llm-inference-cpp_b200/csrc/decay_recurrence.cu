@@ -60,6 +60,35 @@ channel_decay_kernel(const float* __restrict__ low, long ld, int R, const float*
     if (tt < cnt && tok_seq[t0 + tt] >= 0) dec[(size_t)(t0 + tt) * ldd + c] = expf(log_logistic(z[tt]) * inv_tau);
 }
 
+// The same for a handful of tokens, from the second matrix as stored (w2 fp32 [N, R], a channel's R entries side by
+// side): a thread owns one channel of one token and reads its row in 16-byte pieces, all of them under way at once; the
+// sum runs over j in ascending order, as above.
+__global__ void __launch_bounds__(64)
+channel_decay_rows_kernel(const float* __restrict__ low, long ld, int R, const float* __restrict__ w2, const float* __restrict__ bias,
+                          float inv_tau, int N, const int32_t* __restrict__ tok_seq, float* __restrict__ dec, long ldd) {
+  extern __shared__ __align__(16) float low_s[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (tok_seq[t] < 0) return;
+  for (int j = threadIdx.x; j < R; j += blockDim.x) low_s[j] = low[(size_t)t * ld + j];
+  __syncthreads();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= N) return;
+  float z = bias ? bias[c] : 0.f;
+  const float4* row = reinterpret_cast<const float4*>(w2 + (size_t)c * R);
+#pragma unroll 4
+  for (int j4 = 0; j4 < R / 4; ++j4) {
+    const float4 w = row[j4];
+    const float4 l = *reinterpret_cast<const float4*>(low_s + 4 * j4);
+    z = fmaf(w.x, l.x, z);
+    z = fmaf(w.y, l.y, z);
+    z = fmaf(w.z, l.z, z);
+    z = fmaf(w.w, l.w, z);
+  }
+  dec[(size_t)t * ldd + c] = expf(log_logistic(z) * inv_tau);
+}
+
 // x[t, 0:n] = act(x[t, 0:n]) in place; act 0: silu.
 __global__ void __launch_bounds__(256)
 rows_activate_kernel(float* __restrict__ x, long ld, int n, long total, int act) {
@@ -332,10 +361,17 @@ int launch_decay_lanes(const DecaySources& a, int H, int D, int Dv, float* state
 using namespace llmi;
 
 // low: fp32 rows [T, ld] whose first R entries are the low-rank path's first product; w2t fp32 [R, N]; bias fp32 [N] or
-// null; dec fp32 [T, ldd]: dec[t, c] = logistic(bias[c] + sum_j w2t[j, c] low[t, j])^(1/tau).
-LLMI_EXPORT int llmi_channel_decay(const float* low, long ld, int R, const float* w2t, const float* bias, float tau, int N,
-                                   const int32_t* tok_seq, float* dec, long ldd, int n_tokens, cudaStream_t stream) {
+// null; dec fp32 [T, ldd]: dec[t, c] = logistic(bias[c] + sum_j w2t[j, c] low[t, j])^(1/tau).  w2 (optional): the same
+// matrix as stored, fp32 [N, R], for the form of a handful of tokens.
+LLMI_EXPORT int llmi_channel_decay(const float* low, long ld, int R, const float* w2t, const float* w2, const float* bias, float tau,
+                                   int N, const int32_t* tok_seq, float* dec, long ldd, int n_tokens, cudaStream_t stream) {
   if (n_tokens <= 0 || N <= 0 || R <= 0 || R > 4096 || !(tau > 0.f)) return LLMI_ERR_BAD_SIZE;
+  if (n_tokens <= 64 && w2 && R % 4 == 0 && !((uintptr_t)w2 & 15)) {
+    const int cuts = (N + 63) / 64;
+    if (cuts > 65535) return LLMI_ERR_BAD_SIZE;
+    return launch_pdl(PDL_SMALL, channel_decay_rows_kernel, dim3(n_tokens, cuts), dim3(64), (size_t)R * sizeof(float), stream, low, ld,
+                      R, w2, bias, 1.0f / tau, N, tok_seq, dec, ldd);
+  }
   if (n_tokens <= 64) {        // a handful of tokens: a block per token and 64 channels, so that the device has blocks enough
     const int threads = N >= 64 ? 64 : (N + 31) / 32 * 32;
     const int cuts = (N + threads - 1) / threads;

@@ -1494,15 +1494,17 @@ def moe_experts_grouped(h: torch.Tensor, w_gate, w_up, w_down, idx, wt, act: int
 # ---------------------------------------------------------------------------------------------
 # Linear attention with a decay (csrc/decay_recurrence.cu)
 
-def channel_decay(low: torch.Tensor, w2t: torch.Tensor, bias, tau: float, ctx, dec: torch.Tensor) -> None:
+def channel_decay(low: torch.Tensor, w2t: torch.Tensor, bias, tau: float, ctx, dec: torch.Tensor, w2: torch.Tensor | None = None) -> None:
     """dec[t, c] = logistic(bias[c] + sum_j w2t[j, c] * low[t, j]) ** (1 / tau), in fp32 (as exp(log_logistic(z) / tau)).
-    low fp32 [T, R] (a view of wider rows), w2t fp32 [R, N], bias fp32 [N] or None, dec fp32 [T, N]."""
-    _need_cuda(low, w2t, bias, dec)
+    low fp32 [T, R] (a view of wider rows), w2t fp32 [R, N], bias fp32 [N] or None, dec fp32 [T, N].  ``w2`` (optional): the
+    same matrix untransposed, fp32 [N, R]: a handful of tokens read it row by row (the same sums in the same order)."""
+    _need_cuda(low, w2t, bias, dec, w2)
+    assert w2 is None or (w2.dtype == torch.float32 and w2.is_contiguous() and w2.shape == (w2t.shape[1], w2t.shape[0]))
     T, R = low.shape
     N = w2t.shape[1]
     assert low.dtype == w2t.dtype == dec.dtype == torch.float32 and low.stride(1) == 1 and dec.stride(1) == 1
     assert w2t.shape == (R, N) and w2t.is_contiguous() and dec.shape == (T, N) and (bias is None or (bias.dtype == torch.float32 and bias.numel() == N))
-    _check("channel_decay", lib().llmi_channel_decay(_ptr(low), c_long(low.stride(0)), c_int(R), _ptr(w2t), _ptr(bias), c_float(tau),
+    _check("channel_decay", lib().llmi_channel_decay(_ptr(low), c_long(low.stride(0)), c_int(R), _ptr(w2t), _ptr(w2), _ptr(bias), c_float(tau),
                                                      c_int(N), _ptr(ctx.tok_seq), _ptr(dec), c_long(dec.stride(0)), c_int(T), _stream()))
 
 

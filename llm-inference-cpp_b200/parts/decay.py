@@ -76,7 +76,8 @@ class ChannelDecayAttention(_DecayAttention):
             raise ValueError(f"channel_decay_attention: a1 has {self.R} rows but a2 has {tensors['a2'].shape[1]} columns")
         # one product for all projections: rows [q | k | v | gate | low-rank path]
         self.w_in = rt.to_compute(torch.cat([tensors[n] for n in ("q", "k", "v", "g", "a1")], dim=0))
-        self.w2t = rt.to_f32(tensors["a2"]).t().contiguous()          # [rank, heads*dim]: walked in the decay's kernel
+        self.w2 = rt.to_f32(tensors["a2"])                            # [heads*dim, rank]: a handful of tokens read it row by row
+        self.w2t = self.w2.t().contiguous()                           # [rank, heads*dim]: walked by many tokens, eight a block
         self.a_bias = rt.to_f32(tensors["a2.b"])
         self.w_norm = rt.to_f32(tensors["norm"])
         self.w_o = rt.to_compute(tensors["o"])
@@ -88,7 +89,7 @@ class ChannelDecayAttention(_DecayAttention):
         proj = rt.scratch("decay_proj", (T, 2 * N + 2 * Nv + self.R), torch.float32)
         kernels.linear(h, self.w_in, proj, None, kernels.OUT_STORE_F32)
         dec = rt.scratch("decay_w", (T, N), torch.float32)
-        kernels.channel_decay(proj[:, 2 * N + 2 * Nv:], self.w2t, self.a_bias, self.tau, ctx, dec)
+        kernels.channel_decay(proj[:, 2 * N + 2 * Nv:], self.w2t, self.a_bias, self.tau, ctx, dec, self.w2)
         o_raw = rt.scratch("decay_o", (T, Nv), torch.float32)
         kernels.decay_recurrence(proj, 0, N, 2 * N, H, D, Dv, binding.group.data[binding.index], ctx, o_raw, dec=dec,
                                  q_scale=self.q_scale, write_state=binding.writes)

@@ -365,6 +365,10 @@ def test_decays_of_the_key_channels(T, N, R, tau):
     dec = torch.full((T, N), float("nan"), device="cuda:0")
     kernels.channel_decay(torch.tensor(low, device="cuda:0")[:, 2:2 + R], torch.tensor(w2.T.copy(), device="cuda:0"),
                           torch.tensor(b, device="cuda:0"), tau, ctx, dec)
+    dec2 = torch.full((T, N), float("nan"), device="cuda:0")      # with the matrix as stored too: a handful of tokens read that
+    kernels.channel_decay(torch.tensor(low, device="cuda:0")[:, 2:2 + R], torch.tensor(w2.T.copy(), device="cuda:0"),
+                          torch.tensor(b, device="cuda:0"), tau, ctx, dec2, torch.tensor(w2, device="cuda:0"))
+    assert torch.equal(dec, dec2)
     z = low[:, 2:2 + R].astype(np.float64) @ w2.astype(np.float64).T + b
     ref = G.sigmoid(z) ** (1.0 / tau)
     got = dec.cpu().numpy()
