@@ -16,9 +16,9 @@ differ between models of the design:
   - a ``moe`` feed-forward: ``expert.ff``, ``router`` with ``experts``, ``top``, ``scale`` and an optional ``identity``
     (how many further router outputs stand for experts that hand their input on), and an optional ``shared.ff``.
 
-An attention without ``mask`` sees every earlier position, one without ``rot`` is not rotated, one without ``conv`` has
-no convolution, one without ``softcap`` does not cap its scores.  No size has a default: a missing or ill-typed key is
-an error that names it.
+An attention without ``mask`` sees every earlier position, one without ``rot`` (or with ``rot.dims`` 0) is not rotated,
+one without ``conv`` (or with 0 taps) has no convolution, one without ``softcap`` (or with 0) does not cap its scores.
+No size has a default: a missing or ill-typed key is an error that names it.
 """
 from __future__ import annotations
 
@@ -87,6 +87,16 @@ class RenitarLayer:
     mlp: Optional[ExpertsSizes]
 
 
+def _cap(m: Mapping[str, Any], where: str) -> float:
+    """The cap on the scores: absent, null or 0 means none."""
+    if m.get("softcap") is None:
+        return 0.0
+    cap = _number(m, "softcap", where, positive=False)
+    if cap < 0:
+        raise ConfigError(f'config: {where}"softcap" must not be negative')
+    return cap
+
+
 def _block_attention(m: Mapping[str, Any], where: str) -> BlockAttentionSizes:
     heads, kv_heads = _uint(m, "heads", where), _uint(m, "kv_heads", where)
     if heads % kv_heads:
@@ -102,8 +112,8 @@ def _block_attention(m: Mapping[str, Any], where: str) -> BlockAttentionSizes:
             rot_base = _number(rot, "base", where + "rot.")
     return BlockAttentionSizes(
         heads=heads, kv_heads=kv_heads, dim=dim, vdim=_uint(m, "vdim", where), scale=_number(m, "scale", where),
-        taps=_uint(m, "conv", where, MAX_TAPS) if m.get("conv") is not None else 0,
-        softcap=_number(m, "softcap", where) if m.get("softcap") is not None else 0.0,
+        taps=_uint(m, "conv", where, MAX_TAPS, least=0) if m.get("conv") is not None else 0,
+        softcap=_cap(m, where),
         chunk=_uint(_obj(m, "mask", where), "size", where + "mask.", 1 << 30) if m.get("mask") is not None else 0,
         rot_base=rot_base, rot_dims=rot_dims)
 
@@ -112,8 +122,8 @@ def _head_decay(m: Mapping[str, Any], where: str) -> HeadDecaySizes:
     heads = _uint(m, "heads", where)
     decay = m.get("decay")
     if (not isinstance(decay, list) or len(decay) != heads
-            or any(isinstance(d, bool) or not isinstance(d, (int, float)) or not (0.0 <= d <= 1.0) for d in decay)):
-        raise ConfigError(f'config: {where}"decay" must be a list of {heads} numbers in 0..1, one per head')
+            or any(isinstance(d, bool) or not isinstance(d, (int, float)) or not (0.0 <= d < float("inf")) for d in decay)):
+        raise ConfigError(f'config: {where}"decay" must be a list of {heads} numbers that are not negative, one per head')
     return HeadDecaySizes(heads=heads, dim=_uint(m, "dim", where), vdim=_uint(m, "vdim", where),
                           decay=tuple(float(d) for d in decay))
 

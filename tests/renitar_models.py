@@ -75,7 +75,11 @@ WIDE = config(128, 300, [(gla(2, 64, 64, 12.0), moe(64, 8, 2, scale=1.25, identi
 ODD = config(36, 77, [(gla(5, 6, 7, 3.0), moe(10, 3, 2, scale=1.3, identity=1, shared=7)),
                       (pair(att(5, 5, 6, 9, conv=3, chunk=11, rot_dims=2, base=50.0, softcap=7.0), lin(5, 3, [0.8, 0.6, 0.9])), moe(22, 5, 2, scale=0.9))],
              eps=1e-6, mult=0.9)
-CONFIGS = {"gla": GLA, "gla_lanes": GLA_LANES, "pair": PAIR, "pair_bare": PAIR_BARE, "experts": EXPERTS, "mixed": MIXED,
+# a width and sizes that are no multiples of four: nothing is aligned to 16 bytes
+UNALIGNED = config(50, 101, [(gla(3, 7, 9, 6.0), moe(11, 3, 2, scale=1.1, identity=2, shared=13)),
+                             (pair(att(2, 1, 10, 6, conv=2, chunk=9, rot_dims=6, softcap=9.0), lin(5, 7, [0.7, 0.93])), moe(9, 2, 1, scale=1.7))],
+                   mult=0.6)
+CONFIGS = {"unaligned": UNALIGNED, "gla": GLA, "gla_lanes": GLA_LANES, "pair": PAIR, "pair_bare": PAIR_BARE, "experts": EXPERTS, "mixed": MIXED,
            "wide": WIDE, "odd": ODD}
 
 

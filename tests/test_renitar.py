@@ -25,12 +25,16 @@ def test_configuration_reads_every_size_and_refuses_what_is_missing():
     assert c.layers[2].mlp.identity == 0 and c.layers[2].mlp.shared_ff == 0
     bare = parse_config(M.PAIR_BARE)[1].layers[0].mixer.left
     assert (bare.taps, bare.chunk, bare.rot_dims, bare.softcap) == (0, 0, 0, 0.0)
+    zeros = copy.deepcopy(M.PAIR)                      # 0 says "none" as well as a missing key does
+    zeros["layers"][0]["mixer"]["left"].update(conv=0, softcap=0, rot={"dims": 0})
+    z = parse_config(zeros)[1].layers[0].mixer.left
+    assert (z.taps, z.rot_dims, z.softcap) == (0, 0, 0.0)
     for path, value in ((("width",), None), (("residual_mult",), None), (("norm",), {}), (("layers", 0, "type"), "delta"),
                         (("layers", 0, "mixer", "left", "heads"), 0), (("layers", 0, "mixer", "left", "kv_heads"), 3),
                         (("layers", 0, "mixer", "left", "rot", "dims"), 14), (("layers", 0, "mixer", "left", "rot", "dims"), 5),
                         (("layers", 0, "mixer", "left", "scale"), "x"), (("layers", 0, "mixer", "left", "mask", "size"), 0),
-                        (("layers", 0, "mixer", "left", "conv"), 0), (("layers", 0, "mixer", "left", "softcap"), -1.0),
-                        (("layers", 0, "mixer", "right", "decay"), [0.5, 0.5]), (("layers", 0, "mixer", "right", "decay"), [0.5, 0.5, 1.5]),
+                        (("layers", 0, "mixer", "left", "conv"), 17), (("layers", 0, "mixer", "left", "softcap"), -1.0),
+                        (("layers", 0, "mixer", "right", "decay"), [0.5, 0.5]), (("layers", 0, "mixer", "right", "decay"), [0.5, 0.5, -0.5]),
                         (("layers", 0, "mixer", "right"), None), (("layers", 1, "mixer", "tau"), 0), (("layers", 1, "mixer", "vdim"), None),
                         (("layers", 0, "mlp", "router", "top"), 8), (("layers", 0, "mlp", "kind"), "dense"),
                         (("layers", 0, "mlp", "router", "scale"), None), (("layers", 0, "mlp", "expert"), None)):

@@ -85,7 +85,7 @@ def test_prompt_then_token_by_token(loaded, name, dtype):
 
 
 @pytest.mark.parametrize("portion", [2, 3, 7, 64, 100])
-@pytest.mark.parametrize("name", ["gla", "gla_lanes", "pair", "pair_bare", "experts", "mixed", "wide"])
+@pytest.mark.parametrize("name", ["unaligned", "gla", "gla_lanes", "pair", "pair_bare", "experts", "mixed", "wide"])
 def test_prompts_in_portions(loaded, name, portion):
     """A portion's first rows take the convolution's taps from the rows the portion before left, its recurrences go on
     from the states, and blocks of positions are counted from the sequence's start, not the portion's."""
@@ -104,7 +104,7 @@ def test_prompts_in_portions_bf16(loaded, name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["pair", "experts", "mixed", "wide", "odd"])
+@pytest.mark.parametrize("name", ["unaligned", "pair", "experts", "mixed", "wide", "odd"])
 def test_unequal_batches_one_after_another(loaded, name, dtype):
     """Batches of four requests of unequal lengths, prompts of unequal parts of them, decoded together; the next batch
     takes the slots (states, convolution rows) and pages that the one before gave back."""
