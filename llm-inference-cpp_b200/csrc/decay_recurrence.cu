@@ -129,7 +129,10 @@ struct DecaySources {
   long ldw;
   const float* head_decay;   // [H] or null
   float q_scale;
+  int silu_in;               // q, k, v pass silu as they are read (a step of a handful of tokens: no pass of its own over the rows)
 };
+
+__device__ __forceinline__ float decay_silu(float v) { return v / (1.0f + expf(-v)); }
 
 // The general form: one block per (head, sequence), one thread per column j of S, the column in shared memory
 // (S_s[d][cols]: no two threads share a bank); any D and Dv.  The vectors of the next token are fetched while the
@@ -160,8 +163,8 @@ decay_recurrence_kernel(DecaySources a, int H, int D, int Dv, float* __restrict_
     float* dst = vec + buf * 3 * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
       dst[d] = a.dec ? a.dec[(size_t)(r0 + i) * a.ldw + (size_t)h * D + d] : wh;
-      dst[D + d] = xr[a.k_off + d];
-      dst[2 * D + d] = xr[a.q_off + d];
+      dst[D + d] = a.silu_in ? decay_silu(xr[a.k_off + d]) : xr[a.k_off + d];
+      dst[2 * D + d] = a.silu_in ? decay_silu(xr[a.q_off + d]) : xr[a.q_off + d];
     }
   };
   fetch(0, 0);
@@ -169,7 +172,8 @@ decay_recurrence_kernel(DecaySources a, int H, int D, int Dv, float* __restrict_
     __syncthreads();                                         // buffer i&1 is filled; the other one is read out
     if (i + 1 < n) fetch(i + 1, (i + 1) & 1);
     if (!live) continue;
-    const float v = a.proj[(size_t)(r0 + i) * a.ld + a.v_off + (size_t)h * Dv + j];
+    float v = a.proj[(size_t)(r0 + i) * a.ld + a.v_off + (size_t)h * Dv + j];
+    if (a.silu_in) v = decay_silu(v);
     const float* w = vec + (i & 1) * 3 * D;
     const float *k = w + D, *q = w + 2 * D;
     float o = 0.f;
@@ -201,7 +205,7 @@ __device__ __forceinline__ void decay_cp16(void* dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
 }
 
-template <int NI, bool SCALAR>
+template <int NI, bool SCALAR, bool SILU>
 __global__ void __launch_bounds__(256)
 decay_recurrence_lanes_kernel(DecaySources a, int H, int D, int Dv, float* __restrict__ state, long state_stride,
                               const int32_t* __restrict__ seq_q_start, const int32_t* __restrict__ seq_slot,
@@ -277,14 +281,23 @@ decay_recurrence_lanes_kernel(DecaySources a, int H, int D, int Dv, float* __res
     const int t0 = st * DECAY_TOK, cnt = min(DECAY_TOK, n - t0);
     float part[2 * DECAY_TOK];                               // my part of S . q: [token][column]
     auto token = [&](const float* in, float& p0, float& p1) {
-      const float2 v = *reinterpret_cast<const float2*>(in + NVEC * D + 2 * cg);
+      float2 v = *reinterpret_cast<const float2*>(in + NVEC * D + 2 * cg);
+      if (SILU) v = make_float2(decay_silu(v.x), decay_silu(v.y));
       float2 o2 = make_float2(0.f, 0.f), o3 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < NI; ++c) {
         const float4 ww = SCALAR ? make_float4(wh, wh, wh, wh) : (holds[c] ? *reinterpret_cast<const float4*>(in + 64 * c + 4 * sub) : zero);
         const float4 kk = holds[c] ? *reinterpret_cast<const float4*>(in + (NVEC - 2) * D + 64 * c + 4 * sub) : zero;
         const float4 qq = holds[c] ? *reinterpret_cast<const float4*>(in + (NVEC - 1) * D + 64 * c + 4 * sub) : zero;
-        const float we[4] = {ww.x, ww.y, ww.z, ww.w}, ke[4] = {kk.x, kk.y, kk.z, kk.w}, qe[4] = {qq.x, qq.y, qq.z, qq.w};
+        const float we[4] = {ww.x, ww.y, ww.z, ww.w};
+        float ke[4] = {kk.x, kk.y, kk.z, kk.w}, qe[4] = {qq.x, qq.y, qq.z, qq.w};
+        if (SILU) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            ke[e] = decay_silu(ke[e]);
+            qe[e] = decay_silu(qe[e]);
+          }
+        }
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float2 s = S_r[c][e];
@@ -339,7 +352,7 @@ decay_recurrence_lanes_kernel(DecaySources a, int H, int D, int Dv, float* __res
   }
 }
 
-template <int NI, bool SCALAR>
+template <int NI, bool SCALAR, bool SILU>
 int launch_decay_lanes(const DecaySources& a, int H, int D, int Dv, float* state, long state_stride, const int32_t* seq_q_start,
                        const int32_t* seq_slot, float* o_raw, long ldo, int n_seqs, int write_state, cudaStream_t stream) {
   // columns per block: 32, or 16 where that gives the device more blocks than it has SMs to fill (the chain over a
@@ -348,11 +361,11 @@ int launch_decay_lanes(const DecaySources& a, int H, int D, int Dv, float* state
   const size_t smem = (size_t)DECAY_RING * DECAY_TOK * ((SCALAR ? 2 : 3) * D + CB) * sizeof(float);
   static PerDevice<size_t> allowed;
   if (smem > 48 * 1024 && allowed.here() < smem) {
-    if (cudaFuncSetAttribute(decay_recurrence_lanes_kernel<NI, SCALAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(decay_recurrence_lanes_kernel<NI, SCALAR, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return LLMI_ERR_BAD_SIZE;
     allowed.here() = smem;
   }
-  return launch_pdl(PDL_ATTENTION, decay_recurrence_lanes_kernel<NI, SCALAR>, dim3(H, n_seqs, Dv / CB), dim3(8 * CB), smem, stream,
+  return launch_pdl(PDL_ATTENTION, decay_recurrence_lanes_kernel<NI, SCALAR, SILU>, dim3(H, n_seqs, Dv / CB), dim3(8 * CB), smem, stream,
                     a, H, D, Dv, state, state_stride, seq_q_start, seq_slot, o_raw, ldo, write_state);
 }
 
@@ -411,25 +424,27 @@ LLMI_EXPORT int llmi_rows_activate(float* x, long ld, int n, int n_rows, int act
 
 // proj fp32 [T, ld]: q at column q_off, k at k_off (H*D each), v at v_off (H*Dv); the decay: dec fp32 [T, ldw] (H*D a
 // row, a factor per key channel) or head_decay fp32 [H] (one factor per head) — exactly one of the two;
-// state fp32 [slots, state_stride >= H*D*Dv]; o_raw fp32 [T, ldo] receives q_scale * Sᵀ q.
+// state fp32 [slots, state_stride >= H*D*Dv]; o_raw fp32 [T, ldo] receives q_scale * Sᵀ q.  silu_in: q, k, v are read
+// through silu (the same values as after llmi_rows_activate on the rows).
 LLMI_EXPORT int llmi_decay_recurrence(const float* proj, long ld, int q_off, int k_off, int v_off, const float* dec, long ldw,
                                       const float* head_decay, float q_scale, int H, int D, int Dv, float* state,
                                       long state_stride, const int32_t* seq_q_start, const int32_t* seq_slot, float* o_raw,
-                                      long ldo, int n_seqs, int write_state, cudaStream_t stream) {
+                                      long ldo, int n_seqs, int write_state, int silu_in, cudaStream_t stream) {
   if (n_seqs <= 0 || n_seqs > 65535 || H <= 0 || H > 65535 || D <= 0 || Dv <= 0 || Dv > 1024) return LLMI_ERR_BAD_SIZE;
   if ((dec == nullptr) == (head_decay == nullptr)) return LLMI_ERR_UNSUPPORTED;
-  const DecaySources a{proj, ld, q_off, k_off, v_off, dec, ldw, head_decay, q_scale};
+  const DecaySources a{proj, ld, q_off, k_off, v_off, dec, ldw, head_decay, q_scale, silu_in};
   const bool aligned = ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && v_off % 4 == 0 && ldo % 4 == 0 && state_stride % 4 == 0 &&
                        !((uintptr_t)state & 15) && !((uintptr_t)o_raw & 15) && !((uintptr_t)proj & 15) &&
                        (!dec || (ldw % 4 == 0 && !((uintptr_t)dec & 15)));
   if (aligned && D % 4 == 0 && D <= 128 && Dv % 16 == 0) {
-#define LLMI_LANES(NI)                                                                                                          \
-  return dec ? launch_decay_lanes<NI, false>(a, H, D, Dv, state, state_stride, seq_q_start, seq_slot, o_raw, ldo, n_seqs,      \
-                                              write_state, stream)                                                              \
-             : launch_decay_lanes<NI, true>(a, H, D, Dv, state, state_stride, seq_q_start, seq_slot, o_raw, ldo, n_seqs,       \
-                                             write_state, stream)
-    if (D <= 64) LLMI_LANES(1);
-    LLMI_LANES(2);
+#define LLMI_LANES(NI, SC, SI)                                                                                             \
+  return launch_decay_lanes<NI, SC, SI>(a, H, D, Dv, state, state_stride, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream)
+    if (D <= 64) {
+      if (silu_in) { if (dec) LLMI_LANES(1, false, true); else LLMI_LANES(1, true, true); }
+      if (dec) LLMI_LANES(1, false, false); else LLMI_LANES(1, true, false);
+    }
+    if (silu_in) { if (dec) LLMI_LANES(2, false, true); else LLMI_LANES(2, true, true); }
+    if (dec) LLMI_LANES(2, false, false); else LLMI_LANES(2, true, false);
 #undef LLMI_LANES
   }
   const int cols = (Dv + 31) / 32 * 32;

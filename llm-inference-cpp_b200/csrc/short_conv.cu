@@ -211,9 +211,62 @@ norm_conv_token_kernel(const float* __restrict__ x, const float* __restrict__ no
   }
 }
 
+// A step in which every sequence brings ONE token, fp32 rows, the convolution alone (the input itself is not added)
+// and the state's update in one kernel, one thread per (token, channel): the taps are added oldest first as in
+// conv_add_kernel, and the thread that owns a channel reads its state entries before it writes them — the results of
+// llmi_conv_add (without the input) + llmi_conv_carry.
+__global__ void __launch_bounds__(256)
+conv_token_kernel(const float* __restrict__ h, long ldh, const float* __restrict__ w, float* carry_all, long carry_stride,
+                  const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ seq_slot, float* __restrict__ y, long ldy, int C,
+                  int K, int write_state) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int seq = tok_seq[t];
+  const int slot = seq < 0 ? -1 : seq_slot[seq];
+  if (slot < 0) {
+    y[(size_t)t * ldy + c] = 0.f;
+    return;
+  }
+  float* carry = carry_all + (size_t)slot * carry_stride;
+  float old[CONV_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+    if (j < K - 1) old[j] = carry[(size_t)j * C + c];          // all of my state first: independent loads, and read before written
+  const float x = h[(size_t)t * ldh + c];
+  float acc = 0.f;
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+    if (j < K - 1) acc = fmaf(old[j], w[(size_t)j * C + c], acc);
+  acc = fmaf(x, w[(size_t)(K - 1) * C + c], acc);
+  y[(size_t)t * ldy + c] = acc;
+  if (write_state && K > 1) {
+#pragma unroll
+    for (int j = 1; j < CONV_MAX_TAPS - 1; ++j)
+      if (j < K - 1) carry[(size_t)(j - 1) * C + c] = old[j];
+    carry[(size_t)(K - 2) * C + c] = x;
+  }
+}
+
 }  // namespace llmi
 
 using namespace llmi;
+
+// For a step of single tokens: y [T, C] fp32 = conv(h) (the input itself not added) of the fp32 rows h, and the state
+// brought up to date.  A state entry before a sequence's start is zero (a slot's state is cleared when it is handed
+// out), so the taps that reach before position 0 add nothing.
+LLMI_EXPORT int llmi_conv_token(const float* h, long ldh, const float* w, float* carry, long carry_stride, const int32_t* tok_seq,
+                                const int32_t* seq_slot, float* y, long ldy, int n_tokens, int C, int K, int write_state,
+                                cudaStream_t stream) {
+  if (n_tokens <= 0 || C <= 0 || K < 1 || K > CONV_MAX_TAPS) return LLMI_ERR_BAD_SIZE;
+  const int threads = C >= 1024 ? 256 : (C >= 256 ? 128 : 64);
+  const dim3 grid(n_tokens, (C + threads - 1) / threads);
+  if (grid.y > 65535) return LLMI_ERR_BAD_SIZE;
+  return launch_pdl(PDL_SMALL, conv_token_kernel, grid, dim3(threads), 0, stream, h, ldh, w, carry, carry_stride, tok_seq, seq_slot,
+                    y, ldy, C, K, write_state);
+}
 
 // For a step of single tokens: y [T, C] (type `dtype`) = h + conv(h) with h the RMS norm of the fp32 rows x [T, C]
 // (contiguous), and the state brought up to date.

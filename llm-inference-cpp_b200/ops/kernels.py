@@ -1120,6 +1120,21 @@ def conv_add(h: torch.Tensor, w: torch.Tensor, carry: torch.Tensor, ctx, out: to
                                                    _ptr(ctx.seq_slot), c_int(ctx.n_seqs), c_int(C), c_int(K), _stream()))
 
 
+def conv_token(h: torch.Tensor, w: torch.Tensor, carry: torch.Tensor, ctx, out: torch.Tensor, write_state: bool = True) -> None:
+    """For a step in which every sequence brings one token: out = conv(h) (the input itself not added; fp32 rows, ``h`` may be
+    a view of wider rows) and ``carry`` brought up to date — the results of :func:`conv_add` with ``add_input`` False in
+    one kernel.  Relies on a slot's state being zero where a sequence has no earlier positions."""
+    _need_cuda(h, w, carry, out)
+    T, C = h.shape
+    K = w.shape[0]
+    assert h.dtype == out.dtype == torch.float32 and h.stride(1) == 1 and out.stride(1) == 1 and out.shape == (T, C)
+    assert w.dtype == torch.float32 and w.shape == (K, C) and w.is_contiguous()
+    assert carry.dtype == torch.float32 and carry.dim() == 2 and carry.stride(1) == 1 and carry.shape[1] >= (K - 1) * C
+    _check("conv_token", lib().llmi_conv_token(_ptr(h), c_long(h.stride(0)), _ptr(w), _ptr(carry), c_long(carry.stride(0)),
+                                               _ptr(ctx.tok_seq), _ptr(ctx.seq_slot), _ptr(out), c_long(out.stride(0)), c_int(T),
+                                               c_int(C), c_int(K), c_int(1 if write_state else 0), _stream()))
+
+
 def norm_conv_token(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w: torch.Tensor, carry: torch.Tensor, ctx,
                     out: torch.Tensor, write_state: bool = True) -> None:
     """For a step in which every sequence brings one token: out = h + conv(h) with h = rmsnorm(x) (rounded to out's type
@@ -1517,8 +1532,9 @@ def rows_silu(x: torch.Tensor) -> None:
 
 def decay_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, H: int, D: int, Dv: int, state: torch.Tensor, ctx,
                      o_raw: torch.Tensor, dec: torch.Tensor | None = None, head_decay: torch.Tensor | None = None,
-                     q_scale: float = 1.0, write_state: bool = True) -> None:
-    """Per sequence and head, over the step's tokens:  S <- diag(w) S + k v^T,  o = q_scale * S^T q.  q, k (H*D entries) and
+                     q_scale: float = 1.0, write_state: bool = True, silu_in: bool = False) -> None:
+    """Per sequence and head, over the step's tokens:  S <- diag(w) S + k v^T,  o = q_scale * S^T q.  With ``silu_in`` q, k
+    and v pass silu as they are read (for a handful of tokens: no pass of its own over the rows, the same values).  q, k (H*D entries) and
     v (H*Dv) lie in the fp32 rows ``proj`` at the given column offsets; w is ``dec`` fp32 [T, H*D] (a factor per key channel
     and token) or ``head_decay`` fp32 [H] (one constant factor per head).  ``state`` fp32 [slots, >= H*D*Dv] holds S column
     by column and is continued; ``o_raw`` fp32 [T, H*Dv]."""
@@ -1534,7 +1550,7 @@ def decay_recurrence(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, H: 
         _ptr(proj), c_long(proj.stride(0)), c_int(q_off), c_int(k_off), c_int(v_off), _ptr(dec),
         c_long(dec.stride(0) if dec is not None else 0), _ptr(head_decay), c_float(q_scale), c_int(H), c_int(D), c_int(Dv),
         _ptr(state), c_long(state.stride(0)), _ptr(ctx.seq_q_start), _ptr(ctx.seq_slot), _ptr(o_raw), c_long(o_raw.stride(0)),
-        c_int(ctx.n_seqs), c_int(1 if write_state else 0), _stream()))
+        c_int(ctx.n_seqs), c_int(1 if write_state else 0), c_int(1 if silu_in else 0), _stream()))
 
 
 # ---------------------------------------------------------------------------------------------

@@ -445,7 +445,10 @@ class GatedAttention(_MapsAttention):
                 carry = cb.group.data[cb.index]
             else:
                 carry = rt.scratch("attn_conv_none", (1, 1), torch.float32)
-            kernels.conv_add(proj[:, :self.n_qkv], self.conv_w, carry, ctx, qkv, write_state=binding.writes, add_input=False)
+            if ctx.decode and self.taps > 1:      # single tokens: the convolution and its state's update in one kernel
+                kernels.conv_token(proj[:, :self.n_qkv], self.conv_w, carry, ctx, qkv, write_state=binding.writes)
+            else:
+                kernels.conv_add(proj[:, :self.n_qkv], self.conv_w, carry, ctx, qkv, write_state=binding.writes, add_input=False)
         g = binding.group
         pages = ctx.pages_of(g)
         k_cache, v_cache = g.k[binding.index], g.v[binding.index]

@@ -103,6 +103,7 @@ class HeadDecayAttention(_DecayAttention):
     """params: ``width``, ``heads``, ``dim``, ``vdim``, ``decay`` (one factor per head), ``eps`` (of the RMS norm over all
     heads).  tensors: ``q``, ``k`` [heads*dim, width], ``v``, ``g`` [heads*vdim, width], ``norm`` [heads*vdim],
     ``o`` [width, heads*vdim]."""
+    SILU_INSIDE_MAX_TOKENS = 64      # up to here a step has no pass of its own for silu on q, k, v
 
     @classmethod
     def declare(cls, spec):
@@ -128,10 +129,12 @@ class HeadDecayAttention(_DecayAttention):
         rt, H, D, Dv, N, Nv = self.rt, self.H, self.D, self.Dv, self.n_qk, self.n_v
         proj = rt.scratch("decay_proj", (T, 2 * N + 2 * Nv), torch.float32)
         kernels.linear(h, self.w_in, proj, None, kernels.OUT_STORE_F32)
-        kernels.rows_silu(proj[:, :2 * N + Nv])
+        few = T <= self.SILU_INSIDE_MAX_TOKENS      # a handful of tokens: the recurrence applies silu as it reads q, k, v
+        if not few:
+            kernels.rows_silu(proj[:, :2 * N + Nv])
         o_raw = rt.scratch("decay_o", (T, Nv), torch.float32)
         kernels.decay_recurrence(proj, 0, N, 2 * N, H, D, Dv, binding.group.data[binding.index], ctx, o_raw,
-                                 head_decay=self.head_decay, write_state=binding.writes)
+                                 head_decay=self.head_decay, write_state=binding.writes, silu_in=few)
         heads = rt.scratch("attn_out", (T, Nv))
         # the norm runs over the whole row: one "head" of heads*vdim entries
         kernels.delta_finish(o_raw, proj[:, 2 * N + Nv:], self.w_norm, self.eps, 1, Nv, ctx, heads, kernels.GATE_SIGMOID)

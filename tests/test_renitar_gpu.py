@@ -394,13 +394,16 @@ def test_convolution_without_its_input_in_portions(C, K):
     wt = torch.tensor(w.T.copy(), device=dev)
     got = [np.zeros((n, C)) for n in lens]
     done = [0, 0]
-    for step in ([20, 3], [1, 1], [2, 3], [1, 0], [21, 0]):
+    for step in ([20, 3], [1, 1], [2, 3], [1, 0], [1, 0], [1, 0], [1, 0], [1, 0], [17, 0]):
         live = [s for s in range(2) if step[s]]
         rows = np.concatenate([u[s][done[s]:done[s] + step[s]] for s in live])
         wide = torch.tensor(np.concatenate([rows, np.full((rows.shape[0], 6), 9.0, np.float32)], axis=1), device=dev)
         ctx = _ctx([step[s] for s in live], [done[s] for s in live], [slots[s] for s in live])
         out = torch.full((rows.shape[0], C), float("nan"), device=dev)
-        kernels.conv_add(wide[:, :C], wt, carry, ctx, out, add_input=False)
+        if all(step[s] == 1 for s in live) and K > 1:      # single tokens: the kernel that also brings the state up to date
+            kernels.conv_token(wide[:, :C], wt, carry, ctx, out)
+        else:
+            kernels.conv_add(wide[:, :C], wt, carry, ctx, out, add_input=False)
         o = out.cpu().numpy()
         at = 0
         for s in live:
