@@ -323,14 +323,14 @@ GEMOSUN_SIZES = {
 # with matrices and two that hand their input on, three a token, a gated shared expert).  The attention's blocks of
 # positions span the whole context of the decode runs, so that it reads as many positions as the other model's.
 def renitar_config(width, heads, kv_heads, dim, r_heads, experts, identity, top, expert_ff, shared, vocab, block, layers=8):
-    gla = {"heads": r_heads, "dim": dim, "vdim": dim, "tau": 16.0, "rank": max(16, width // 32)}
-    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "conv": 4, "softcap": 30.0,
+    gla = {"heads": r_heads, "dim": dim, "vdim": dim, "tau": 8.0, "rank": max(16, width // 32)}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "conv": 4, "softcap": 50.0,
             "mask": {"size": block}, "rot": {"base": 10000.0, "dims": dim // 2}}
     right = {"heads": r_heads, "dim": dim, "vdim": dim, "decay": [1.0 - 2.0 ** (-1.0 - 7.0 * h / max(r_heads - 1, 1)) for h in range(r_heads)]}
-    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "identity": identity, "top": top, "scale": 1.5},
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "identity": identity, "top": top, "scale": 2.0},
            "shared": {"ff": shared}}
     kinds = [("gla", gla), ("parallel", {"left": left, "right": right})]
-    return {"architecture": "Renitar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+    return {"architecture": "Renitar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
             "layers": [{"type": kinds[i % 2][0], "mixer": kinds[i % 2][1], "mlp": moe} for i in range(layers)]}
 
 

@@ -188,7 +188,7 @@ decay_recurrence_kernel(DecaySources a, int H, int D, int Dv, float* __restrict_
     for (int d = 0; d < D; ++d) S_g[(size_t)j * D + d] = S_s[(size_t)d * cols + j];
 }
 
-// The form for D a multiple of 4 up to 128 and Dv a multiple of 16.  A thread holds TWO neighbouring columns of S and
+// The form for D a multiple of 4 up to 256 and Dv a multiple of 16.  A thread holds TWO neighbouring columns of S and
 // a sixteenth of their entries (lane `sub` of sixteen: d = 64 i + 4 sub + 0..3, while d < D) in registers; the partial
 // sums of o over d of a stage's eight tokens (sixteen numbers a thread) are joined over the sixteen lanes at the stage's
 // end by a butterfly that halves what a lane keeps in every round (fifteen shuffles for eight tokens; lane i ends up
@@ -245,25 +245,35 @@ decay_recurrence_lanes_kernel(DecaySources a, int H, int D, int Dv, float* __res
   const float* q_src = a.proj + a.q_off + (size_t)h * D;
   const float* w_src = SCALAR ? nullptr : a.dec + (size_t)h * D;
   const int n_stages = (n + DECAY_TOK - 1) / DECAY_TOK;
-  // a token's entry has at most 3 * 32 + 8 pieces, fewer than the block has threads: thread e copies piece e of every
-  // token, from an address that moves by one row a token
-  const float* my_src = nullptr;
-  long my_step = 0;
-  if ((int)threadIdx.x < n16) {
-    const int e = threadIdx.x, part = e / Q, off = 4 * (e - part * Q);
+  // a token's entry has at most 3 * 32 + 8 pieces (NI <= 2), fewer than the block has threads, or 3 * 64 + 8 (NI = 4), no
+  // more than twice as many: thread e copies piece e (and e + blockDim.x) of every token, from an address that moves by
+  // one row a token
+  constexpr int SLOTS = NI > 2 ? 2 : 1;
+  const float* my_src[SLOTS];
+  long my_step[SLOTS];
+#pragma unroll
+  for (int u = 0; u < SLOTS; ++u) {
+    my_src[u] = nullptr;
+    my_step[u] = 0;
+    const int e = threadIdx.x + u * blockDim.x;
+    if (e >= n16) continue;
+    const int part = e / Q, off = 4 * (e - part * Q);
     const int which = SCALAR ? part + 1 : part;              // 0: w, 1: k, 2: q, 3: v
-    my_step = which == 0 ? a.ldw : a.ld;
-    my_src = (which == 0 ? w_src + off : which == 1 ? k_src + off : which == 2 ? q_src + off : v_src + 4 * (e - NVEC * Q)) +
-             (size_t)r0 * my_step;
+    my_step[u] = which == 0 ? a.ldw : a.ld;
+    my_src[u] = (which == 0 ? w_src + off : which == 1 ? k_src + off : which == 2 ? q_src + off : v_src + 4 * (e - NVEC * Q)) +
+                (size_t)r0 * my_step[u];
   }
   auto issue = [&](int st) {
-    if (!my_src) return;
-    float* dst = sm + (size_t)(st % DECAY_RING) * DECAY_TOK * pitch + 4 * threadIdx.x;
     const int t0 = st * DECAY_TOK, cnt = min(DECAY_TOK, n - t0);
-    const float* src = my_src + (size_t)t0 * my_step;
 #pragma unroll
-    for (int tk = 0; tk < DECAY_TOK; ++tk)
-      if (tk < cnt) decay_cp16(dst + (size_t)tk * pitch, src + (size_t)tk * my_step);
+    for (int u = 0; u < SLOTS; ++u) {
+      if (!my_src[u]) continue;
+      float* dst = sm + (size_t)(st % DECAY_RING) * DECAY_TOK * pitch + 4 * (threadIdx.x + u * blockDim.x);
+      const float* src = my_src[u] + (size_t)t0 * my_step[u];
+#pragma unroll
+      for (int tk = 0; tk < DECAY_TOK; ++tk)
+        if (tk < cnt) decay_cp16(dst + (size_t)tk * pitch, src + (size_t)tk * my_step[u]);
+    }
   };
 #pragma unroll
   for (int s = 0; s < DECAY_RING - 1; ++s) {
@@ -436,15 +446,19 @@ LLMI_EXPORT int llmi_decay_recurrence(const float* proj, long ld, int q_off, int
   const bool aligned = ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && v_off % 4 == 0 && ldo % 4 == 0 && state_stride % 4 == 0 &&
                        !((uintptr_t)state & 15) && !((uintptr_t)o_raw & 15) && !((uintptr_t)proj & 15) &&
                        (!dec || (ldw % 4 == 0 && !((uintptr_t)dec & 15)));
-  if (aligned && D % 4 == 0 && D <= 128 && Dv % 16 == 0) {
+  if (aligned && D % 4 == 0 && D <= 256 && Dv % 16 == 0) {
 #define LLMI_LANES(NI, SC, SI)                                                                                             \
   return launch_decay_lanes<NI, SC, SI>(a, H, D, Dv, state, state_stride, seq_q_start, seq_slot, o_raw, ldo, n_seqs, write_state, stream)
     if (D <= 64) {
       if (silu_in) { if (dec) LLMI_LANES(1, false, true); else LLMI_LANES(1, true, true); }
       if (dec) LLMI_LANES(1, false, false); else LLMI_LANES(1, true, false);
     }
-    if (silu_in) { if (dec) LLMI_LANES(2, false, true); else LLMI_LANES(2, true, true); }
-    if (dec) LLMI_LANES(2, false, false); else LLMI_LANES(2, true, false);
+    if (D <= 128) {
+      if (silu_in) { if (dec) LLMI_LANES(2, false, true); else LLMI_LANES(2, true, true); }
+      if (dec) LLMI_LANES(2, false, false); else LLMI_LANES(2, true, false);
+    }
+    if (silu_in) { if (dec) LLMI_LANES(4, false, true); else LLMI_LANES(4, true, true); }
+    if (dec) LLMI_LANES(4, false, false); else LLMI_LANES(4, true, false);
 #undef LLMI_LANES
   }
   const int cols = (Dv + 31) / 32 * 32;

@@ -13,7 +13,7 @@ import math
 
 import torch
 
-from ..cache.storage import KVRequest
+from ..cache.storage import KVRequest, StateRequest
 from ..ops import kernels
 from .registry import TensorDecl, nested_build, nested_declare, part
 
@@ -426,7 +426,6 @@ class GatedAttention(_MapsAttention):
     def more_cache_requests(self):
         if self.taps <= 1:
             return {}
-        from ..cache.storage import StateRequest
         return {"conv": StateRequest(((self.taps - 1) * self.n_qkv,), torch.float32)}
 
     def weight_bytes(self) -> int:

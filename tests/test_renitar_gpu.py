@@ -299,7 +299,8 @@ def test_attention_sees_its_block_of_positions(chunk, key, sizes, dtype):
         assert alone == G.sees(299, key, chunk), (key, chunk)
 
 
-@pytest.mark.parametrize("H_,D,Dv", [(2, 64, 64), (3, 12, 20), (2, 40, 32), (1, 96, 48), (4, 128, 16), (2, 4, 12), (1, 200, 8), (5, 6, 7)])
+@pytest.mark.parametrize("H_,D,Dv", [(2, 64, 64), (3, 12, 20), (2, 40, 32), (1, 96, 48), (4, 128, 16), (2, 4, 12), (1, 200, 8), (5, 6, 7),
+                                     (1, 256, 32), (2, 160, 16)])
 @pytest.mark.parametrize("per_head", [False, True])
 def test_recurrence_with_a_decay(H_, D, Dv, per_head):
     """S <- w S + k v^T, o = scale S^T q for three sequences of unequal lengths in slots that are not in order, cut into
